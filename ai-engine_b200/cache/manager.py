@@ -90,7 +90,7 @@ class PagedCache:
         for n in self.requests:
             self.roles.setdefault(n.run, []).append(n.role)
         h = host()
-        self.book = h.CacheManager([h.GroupSpec(g.page_size, g.num_pages, g.request.window)
+        self.book = h.CacheManager([h.GroupSpec(g.page_size, g.num_pages, g.request.window, g.request.keep_first)
                                     for g in self.groups], self.max_seqs, self.max_pages_per_seq)
         self.state: Dict[Tuple[int, str], torch.Tensor] = {}
         if allocate:

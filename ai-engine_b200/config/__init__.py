@@ -12,3 +12,6 @@ __all__.append("PifutarConfig")
 from .zupitar import ZupitarConfig  # noqa: E402
 
 __all__.append("ZupitarConfig")
+from .tizodra import TizodraConfig  # noqa: E402
+
+__all__.append("TizodraConfig")

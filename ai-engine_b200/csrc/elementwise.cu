@@ -425,3 +425,125 @@ extern "C" int aie_scaled_sum(const float* a, int pa, float sa, const float* b, 
     scaled_sum_kernel<<<blocks, 256, 0, stream>>>(a, pa, sa, b, pb, sb, out, (size_t)n);
     AIE_LAUNCH_CHECK();
 }
+
+// ---------------------------------------------------------------------------
+// out = act(z) element by element for a feed-forward without a gate.  act: 0 silu, 1 relu, 2 gelu (tanh form),
+// 3 the square of relu.  Computed in float32, rounded once.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float plain_act(float z, int act) {
+    if (act == 1) return fmaxf(z, 0.f);
+    if (act == 3) {
+        const float r = fmaxf(z, 0.f);
+        return r * r;
+    }
+    if (act == 2) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    return z / (1.f + expf(-z));
+}
+
+template <typename I, typename O>
+__global__ void activate_kernel(const I* __restrict__ z, O* __restrict__ out, size_t n, int act) {
+    size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    const size_t stride = (size_t)gridDim.x * blockDim.x * 4;
+    for (; i + 3 < n; i += stride) {
+        float4 v = load4<I>(z + i);
+        v.x = plain_act(v.x, act); v.y = plain_act(v.y, act); v.z = plain_act(v.z, act); v.w = plain_act(v.w, act);
+        store4<O>(out + i, v);
+    }
+    if (i < n)                                       // the last one to three elements
+        for (size_t j = i; j < n; ++j) out[j] = from_f32<O>(plain_act(to_f32<I>(z[j]), act));
+}
+
+extern "C" int aie_activate(const void* z, int in_dtype, void* out, int out_dtype, long long n, int act,
+                            cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (act < 0 || act > 3) return AIE_BAD_ARG;
+    int blocks = (int)((n / 4 + 256) / 256);
+    if (blocks > aie_sm_count() * 16) blocks = aie_sm_count() * 16;
+    if (in_dtype == AIE_F32 && out_dtype == AIE_F32)
+        activate_kernel<float, float><<<blocks, 256, 0, stream>>>((const float*)z, (float*)out, (size_t)n, act);
+    else if (in_dtype == AIE_F32 && out_dtype == AIE_BF16)
+        activate_kernel<float, bf16><<<blocks, 256, 0, stream>>>((const float*)z, (bf16*)out, (size_t)n, act);
+    else if (in_dtype == AIE_BF16 && out_dtype == AIE_BF16)
+        activate_kernel<bf16, bf16><<<blocks, 256, 0, stream>>>((const bf16*)z, (bf16*)out, (size_t)n, act);
+    else
+        return AIE_BAD_ARG;
+    AIE_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------
+// x <- x * s, float32, in place (logits with a constant factor)
+// ---------------------------------------------------------------------------
+__global__ void scale_kernel(float* __restrict__ x, size_t n, float s) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) x[i] *= s;
+}
+
+extern "C" int aie_scale(float* x, long long n, float s, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    int blocks = (int)((n + 255) / 256);
+    if (blocks > aie_sm_count() * 16) blocks = aie_sm_count() * 16;
+    scale_kernel<<<blocks, 256, 0, stream>>>(x, (size_t)n, s);
+    AIE_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------
+// Sinusoidal position vectors added to the float32 stream: x[t, 2i] += sin(p_t f_i), x[t, 2i + 1] += cos(p_t f_i),
+// the angle float(p) * f_i in float32.  inv_freq holds ceil(D / 2) frequencies.
+// ---------------------------------------------------------------------------
+__global__ void add_sinusoid_kernel(float* __restrict__ x, const int* __restrict__ positions,
+                                    const float* __restrict__ inv_freq, int D, int pairs) {
+    const int t = blockIdx.x;
+    const float p = (float)positions[t];
+    float* row = x + (size_t)t * D;
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        float s, c;
+        sincosf(p * inv_freq[i], &s, &c);
+        row[2 * i] += s;
+        if (2 * i + 1 < D) row[2 * i + 1] += c;
+    }
+}
+
+extern "C" int aie_add_sinusoid(float* x, const int* positions, const float* inv_freq, int T, int D,
+                                cudaStream_t stream) {
+    if (T <= 0 || D <= 0) return 0;
+    add_sinusoid_kernel<<<T, 128, 0, stream>>>(x, positions, inv_freq, D, (D + 1) / 2);
+    AIE_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------
+// Two float32 streams side by side as one row of the compute dtype: out[t] = [x[t] (+ delta[t], or the sum of
+// its parts) | y[t]], the input of a projection that mixes the running stream with an earlier one.
+// ---------------------------------------------------------------------------
+template <typename A, typename O>
+__global__ void join_streams_kernel(const float* __restrict__ x, const A* __restrict__ delta, int parts,
+                                    size_t part_stride, const float* __restrict__ y, O* __restrict__ out, int D,
+                                    size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) {
+        const size_t t = i / D, c = i - t * D;
+        float s = x[i];
+        if (delta != nullptr)
+            for (int p = 0; p < parts; ++p) s += to_f32<A>(delta[(size_t)p * part_stride + i]);
+        out[t * 2 * D + c] = from_f32<O>(s);
+        out[t * 2 * D + D + c] = from_f32<O>(y[i]);
+    }
+}
+
+extern "C" int aie_join_streams(const float* x, const void* delta, int delta_dtype, int parts, long long part_stride,
+                                const float* y, void* out, int out_dtype, int T, int D, cudaStream_t stream) {
+    if (T <= 0 || D <= 0) return 0;
+    const size_t n = (size_t)T * D;
+    int blocks = (int)((n + 255) / 256);
+    if (blocks > aie_sm_count() * 16) blocks = aie_sm_count() * 16;
+#define AIE_JS(A, O)                                                                                         \
+    join_streams_kernel<A, O><<<blocks, 256, 0, stream>>>(x, (const A*)delta, parts, (size_t)part_stride, y, \
+                                                          (O*)out, D, n)
+    const bool dbf = delta != nullptr && delta_dtype == AIE_BF16;
+    if (out_dtype == AIE_F32) { if (dbf) AIE_JS(bf16, float); else AIE_JS(float, float); }
+    else if (out_dtype == AIE_BF16) { if (dbf) AIE_JS(bf16, bf16); else AIE_JS(float, bf16); }
+    else return AIE_BAD_ARG;
+#undef AIE_JS
+    AIE_LAUNCH_CHECK();
+}

@@ -28,12 +28,14 @@ PYBIND11_MODULE(_aie_host, m) {
         .def("release", &PagePool::release);
 
     py::class_<GroupSpec>(m, "GroupSpec")
-        .def(py::init([](int page_size, int num_pages, int window) {
-                 GroupSpec g; g.page_size = page_size; g.num_pages = num_pages; g.window = window; return g;
-             }), py::arg("page_size"), py::arg("num_pages"), py::arg("window") = 0)
+        .def(py::init([](int page_size, int num_pages, int window, int keep_first) {
+                 GroupSpec g; g.page_size = page_size; g.num_pages = num_pages; g.window = window;
+                 g.keep_first = keep_first; return g;
+             }), py::arg("page_size"), py::arg("num_pages"), py::arg("window") = 0, py::arg("keep_first") = 0)
         .def_readwrite("page_size", &GroupSpec::page_size)
         .def_readwrite("num_pages", &GroupSpec::num_pages)
-        .def_readwrite("window", &GroupSpec::window);
+        .def_readwrite("window", &GroupSpec::window)
+        .def_readwrite("keep_first", &GroupSpec::keep_first);
 
     py::class_<CacheManager>(m, "CacheManager")
         .def(py::init<std::vector<GroupSpec>, int, int>(), py::arg("groups"), py::arg("max_seqs"), py::arg("max_pages_per_seq"))
@@ -55,6 +57,7 @@ PYBIND11_MODULE(_aie_host, m) {
         .def("finish", &CacheManager::finish)
         .def("pages", &CacheManager::pages)
         .def("first_live", &CacheManager::first_live)
+        .def("kept_pages", &CacheManager::kept_pages)
         .def("check_invariants", &CacheManager::check_invariants)
         .def("fill_block_table", [](const CacheManager& c, int g, std::vector<int> slots, int width,
                                     py::array_t<int32_t, py::array::c_style> out) {

@@ -72,11 +72,13 @@ struct GroupSpec {
     int page_size = 16;   // tokens per page
     int num_pages = 0;    // pages of this group's pool
     int window = 0;       // 0: every key is kept; w > 0: a query at p reads keys in (p - w, p]
+    int keep_first = 0;   // with a window: keys [0, keep_first) stay readable for every later query
 };
 
 struct SeqTable {
     std::vector<int> pages;  // by page index (pos / page_size); -1 once given back
-    int first_live = 0;      // pages [first_live, pages.size()) are held
+    int first_live = 0;      // pages [first_live, pages.size()) are held, and so are the pages before them that
+                             // hold one of the group's first `keep_first` tokens
 };
 
 class CacheManager {
@@ -88,6 +90,7 @@ class CacheManager {
         for (auto& g : groups_) {
             if (g.page_size <= 0) throw std::invalid_argument("CacheManager: page_size must be positive");
             if (g.window < 0) throw std::invalid_argument("CacheManager: negative window");
+            if (g.keep_first < 0) throw std::invalid_argument("CacheManager: negative keep_first");
             pools_.emplace_back(g.num_pages);
             tables_.emplace_back(max_seqs);
         }
@@ -156,7 +159,7 @@ class CacheManager {
             const int first_key = std::max(0, computed - w + 1);
             auto& t = tables_[g][slot];
             const int stop = std::min<int>(first_key / groups_[g].page_size, (int)t.pages.size());
-            for (int i = t.first_live; i < stop; ++i) {
+            for (int i = std::max(t.first_live, kept_pages(g)); i < stop; ++i) {
                 pools_[g].release(t.pages[i]);
                 t.pages[i] = -1;
                 ++released;
@@ -171,7 +174,8 @@ class CacheManager {
         check_slot(slot);
         for (int g = 0; g < num_groups(); ++g) {
             auto& t = tables_[g][slot];
-            for (int i = t.first_live; i < (int)t.pages.size(); ++i) pools_[g].release(t.pages[i]);
+            for (int i = 0; i < (int)t.pages.size(); ++i)
+                if (t.pages[i] >= 0) pools_[g].release(t.pages[i]);
             t.pages.clear();
             t.first_live = 0;
         }
@@ -185,6 +189,11 @@ class CacheManager {
 
     const std::vector<int>& pages(int g, int slot) const { return tables_.at(g).at(slot).pages; }
     int first_live(int g, int slot) const { return tables_.at(g).at(slot).first_live; }
+    // leading pages of a windowed group that are never given back: those that hold one of its first keep_first tokens
+    int kept_pages(int g) const {
+        const auto& gs = groups_[g];
+        return (gs.keep_first + gs.page_size - 1) / gs.page_size;
+    }
 
     // rows of block tables for a batch: out[i * width + j] = page j of slots[i], -1 beyond
     void fill_block_table(int g, const int* slots, int n, int width, int32_t* out) const {
@@ -210,7 +219,7 @@ class CacheManager {
                     throw std::logic_error("free slot " + std::to_string(s) + " still has pages");
                 for (int i = 0; i < (int)t.pages.size(); ++i) {
                     const int p = t.pages[i];
-                    if (i < t.first_live) {
+                    if (i < t.first_live && i >= kept_pages(g)) {
                         if (p != -1) throw std::logic_error("page behind the window still listed");
                         continue;
                     }
@@ -278,7 +287,8 @@ class Scheduler {
         for (int g = 0; g < cache_->num_groups(); ++g) {
             const auto& gs = cache_->group(g);
             int held = most;
-            if (gs.window > 0) held = std::min(most, gs.window + 2 * gs.page_size + std::min(budget_, most));
+            if (gs.window > 0)
+                held = std::min(most, gs.window + gs.keep_first + 3 * gs.page_size + std::min(budget_, most));
             const int pages = (held + gs.page_size - 1) / gs.page_size;
             if (pages > gs.num_pages || (most + gs.page_size - 1) / gs.page_size > cache_->max_pages_per_seq())
                 return "request can never fit the cache (" + std::to_string(most) + " tokens need " + std::to_string(pages) + " pages of group " + std::to_string(g) + ", pool has " + std::to_string(gs.num_pages) + ")";

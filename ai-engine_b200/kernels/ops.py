@@ -1017,3 +1017,150 @@ def scaled_sum(a: torch.Tensor, sa: float, b: torch.Tensor, sb: float) -> torch.
                                  c_int(b.shape[0] if b.dim() == 3 else 1), c_float(sb), _p(out),
                                  c_longlong(out.numel()), _stream()), "scaled_sum")
     return out
+
+
+# ---------------------------------------------------------------------------
+# parts of layers with a fixed position vector, a feed-forward without a gate, a stream mixed with an earlier one,
+# attention with a sink behind a window, the delta rule
+PLAIN_ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2, "relu_squared": 3}
+
+
+def activate(z: torch.Tensor, activation: str, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """act(z) element by element (silu, relu, gelu_tanh, relu_squared), computed in float32."""
+    _dev(z)
+    out = torch.empty(z.shape, dtype=out_dtype or z.dtype, device=z.device)
+    lib = library("elementwise.cu")
+    with region("activate", _nb(z, out)):
+        check(lib.aie_activate(_p(z), c_int(dtype_code(z)), _p(out), c_int(dtype_code(out)), c_longlong(z.numel()),
+                               c_int(PLAIN_ACTIVATIONS[activation]), _stream()), "activate")
+    return out
+
+
+def linear_activated(x: torch.Tensor, w: torch.Tensor, activation: str, err: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """act(x . w^T) in x's dtype for a feed-forward without a gate."""
+    return activate(linear(x, w, x.dtype, err), activation)
+
+
+def scale_(x: torch.Tensor, s: float) -> torch.Tensor:
+    """x <- x * s in place (float32)."""
+    _dev(x)
+    if x.dtype != torch.float32:
+        raise KernelError("scale_: float32 operand")
+    lib = library("elementwise.cu")
+    with region("scale", 2 * _nb(x)):
+        check(lib.aie_scale(_p(x), c_longlong(x.numel()), c_float(s), _stream()), "scale")
+    return x
+
+
+def add_sinusoid(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor) -> None:
+    """x[t, 2i] += sin(p_t f_i), x[t, 2i + 1] += cos(p_t f_i) in place; x [T, D] float32, inv_freq [ceil(D / 2)]."""
+    _dev(x, positions, inv_freq)
+    T, D = x.shape
+    if x.dtype != torch.float32 or inv_freq.dtype != torch.float32 or inv_freq.shape[0] != (D + 1) // 2:
+        raise KernelError("add_sinusoid: a float32 stream and one frequency per pair of columns")
+    lib = library("elementwise.cu")
+    with region("add_sinusoid", 2 * _nb(x)):
+        check(lib.aie_add_sinusoid(_p(x), _p(positions), _p(inv_freq), c_int(T), c_int(D), _stream()), "add_sinusoid")
+
+
+def join_streams(x: torch.Tensor, delta: Optional[torch.Tensor], y: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """[x (+ delta, or the sum of its parts [parts, T, D]) | y] as rows [T, 2D] of `out_dtype`; x, y float32."""
+    _dev(x, delta, y)
+    T, D = x.shape
+    if x.dtype != torch.float32 or y.dtype != torch.float32 or y.shape != x.shape:
+        raise KernelError("join_streams: two float32 streams of one shape")
+    parts, stride = 0, 0
+    if delta is not None:
+        parts, stride = (delta.shape[0], delta.stride(0)) if delta.dim() == 3 else (1, 0)
+        if delta.shape[-2:] != x.shape:
+            raise KernelError("join_streams: delta differs in shape from x")
+    out = torch.empty((T, 2 * D), dtype=out_dtype, device=x.device)
+    lib = library("elementwise.cu")
+    with region("join_streams", _nb(x, delta, y, out)):
+        check(lib.aie_join_streams(_p(x), _p(delta), c_int(dtype_code(delta) if delta is not None else 0), c_int(parts),
+                                   c_longlong(stride), _p(y), _p(out), c_int(dtype_code(out)), c_int(T), c_int(D),
+                                   _stream()), "join_streams")
+    return out
+
+
+def sink_attn_prepare(proj: torch.Tensor, bias: Optional[torch.Tensor], pages: torch.Tensor, ctx,
+                      block_table: torch.Tensor, H: int, G: int, d: int, e: int, eps: float, write: bool = True):
+    """From a step's fused projection [q (H d) | k (G d) | v (G e) | gate logits (H)] (float32 [T, >= that]):
+    (q [T, H, d] in the cache's dtype with its bias added, gate [T, H] float32 = sigmoid of the logits); with
+    `write`, each token's key (with bias) and its value (with bias, every head divided by its root mean square)
+    go into its cache row [k | v].  pages [num_pages, G, P, d + e]; bias float32 [H d + G d + G e] or None."""
+    _dev(proj, bias, pages, block_table)
+    T, ld = proj.shape
+    if (proj.dtype != torch.float32 or ld < H * d + G * (d + e) + H or pages.shape[1] != G or pages.shape[3] != d + e
+            or (bias is not None and (bias.dtype != torch.float32 or bias.numel() != H * d + G * (d + e)))):
+        raise KernelError("sink_attn_prepare: shapes or dtypes do not fit")
+    q = torch.empty((T, H, d), dtype=pages.dtype, device=proj.device)
+    gate = torch.empty((T, H), dtype=torch.float32, device=proj.device)
+    lib = library("sink_attention.cu")
+    with region("sink_attn_prepare", _nb(proj, q) + T * G * (d + e) * pages.element_size()):
+        check(lib.aie_sink_attn_prepare(_p(proj), c_int(ld), _p(bias), _p(q), c_int(dtype_code(q)), _p(pages),
+                                        c_int(dtype_code(pages)), _p(gate), _p(ctx.positions), _p(ctx.token_req),
+                                        _p(block_table), c_int(block_table.shape[1]), c_int(pages.shape[0]),
+                                        c_int(pages.shape[2]), c_int(T), c_int(H), c_int(G), c_int(d), c_int(e),
+                                        c_float(eps), c_int(1 if write else 0), _p(ctx.err), _stream()),
+              "sink_attn_prepare")
+    return q, gate
+
+
+def sink_attention(q: torch.Tensor, pages: torch.Tensor, gate: Optional[torch.Tensor], temp: Optional[torch.Tensor],
+                   slope: Optional[torch.Tensor], sink: Optional[torch.Tensor], ctx, work, block_table: torch.Tensor,
+                   e: int, scale: float, window: int, keep_first: int) -> torch.Tensor:
+    """Attention of a step's query tokens over cache rows [k (d) | v (e)]:
+    s(i, j) = (q_i . k_j) * scale * temp[h] - slope[h] * (i - j) over the keys j <= i with i - j < window or
+    j < keep_first (window 0: all); softmax whose denominator also holds exp(sink[h]); times gate[i, h].
+    q [T, H, d]; gate [T, H], temp, slope, sink [H] float32 or None.  Returns [T, H, e] in q's dtype."""
+    _dev(q, pages, gate, temp, slope, sink, block_table)
+    T, H, d = q.shape
+    G = pages.shape[1]
+    if pages.shape[3] != d + e or H % G or pages.dtype != q.dtype:
+        raise KernelError("sink_attention: shapes or dtypes do not fit")
+    out = torch.empty((T, H, e), dtype=q.dtype, device=q.device)
+    cost = (0.0, 0.0)
+    if _profiling() and hasattr(ctx, "h_q_len"):
+        ql, cl = ctx.h_q_len.astype(float), ctx.h_ctx_len.astype(float)
+        seen = cl + (ql + 1) / 2
+        if window > 0:
+            seen = seen.clip(max=float(window + keep_first))
+        rows = (cl + ql).clip(max=float(window + keep_first) + ql) if window > 0 else cl + ql
+        cost = (float(rows.sum()) * G * (d + e) * pages.element_size() + _nb(q, out),
+                2.0 * float((ql * seen).sum()) * H * (d + e))
+    lib = library("sink_attention.cu")
+    with region("sink_attention_plain", *cost):
+        check(lib.aie_sink_attention_plain(_p(q), _p(pages), _p(out), c_int(dtype_code(q)), _p(gate), _p(temp), _p(slope),
+                                           _p(sink), _p(ctx.positions), _p(ctx.token_req), _p(block_table),
+                                           c_int(block_table.shape[1]), c_int(pages.shape[0]), c_int(pages.shape[2]),
+                                           c_int(T), c_int(H), c_int(G), c_int(d), c_int(e), c_int(window),
+                                           c_int(keep_first), c_float(scale), _p(None), _p(ctx.err), _stream()),
+              "sink_attention_plain")
+    return out
+
+
+def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, b_raw: torch.Tensor, a_raw: torch.Tensor,
+               a_log: torch.Tensor, dt_bias: torch.Tensor, q_scale: float, unit_eps: float, state: torch.Tensor, ctx,
+               H: int, G: int, d: int, e: int) -> torch.Tensor:
+    """The gated delta rule over a step's tokens, the state [max_seqs, H, d, e] float32 read and left in each
+    request's slot:  q, k made unit vectors per head (x / sqrt(|x|^2 + unit_eps), q times q_scale);
+    beta = sigmoid(b_raw); g = exp(-exp(a_log) softplus(a_raw + dt_bias));  S <- g S;  u = beta (v - S^T k);
+    S <- S + k u^T;  o = S^T q.  q, k [T, G d] and v [T, H e] are float32 views with one row stride; b_raw, a_raw
+    [T, H] float32 views (rows any stride); head h reads q/k head h / (H / G).  Returns o [T, H, e] float32."""
+    _dev(a_log, dt_bias, state)
+    T, ld = q.shape[0], q.stride(0)
+    if (q.dtype != torch.float32 or k.dtype != torch.float32 or v.dtype != torch.float32 or k.stride(0) != ld
+            or v.stride(0) != ld or q.stride(1) != 1 or k.stride(1) != 1 or v.stride(1) != 1
+            or b_raw.dtype != torch.float32 or a_raw.dtype != torch.float32 or b_raw.stride(1) != 1 or a_raw.stride(1) != 1
+            or state.shape[1:] != (H, d, e) or state.dtype != torch.float32 or H % G or d > 256):
+        raise KernelError("delta_rule: shapes or dtypes do not fit")
+    out = torch.empty((T, H, e), dtype=torch.float32, device=q.device)
+    lib = library("delta_rule.cu")
+    with region("delta_rule", _nb(out) + T * (2 * G * d + H * e) * 4 + 2 * ctx.R * H * d * e * 4, 6.0 * T * H * d * e):
+        check(lib.aie_delta_rule(_p(q), _p(k), _p(v), c_int(ld), _p(b_raw), c_int(b_raw.stride(0)), _p(a_raw),
+                                 c_int(a_raw.stride(0)), _p(a_log), _p(dt_bias), c_float(q_scale), c_float(unit_eps),
+                                 _p(state), _p(out), _p(ctx.q_start), _p(ctx.q_len), _p(ctx.slots), _p(ctx.live),
+                                 c_int(ctx.R), c_int(H), c_int(G), c_int(d), c_int(e), c_int(state.shape[0]),
+                                 _p(ctx.err), _stream()), "delta_rule")
+    return out

@@ -6,9 +6,12 @@ from .conv import CausalShortConv
 from .embedding import LMHead, TokenEmbedding
 from .latent_attention import LATENT_WORK, LatentAttention, LatentWork
 from .linear_attention import DecayLinearAttention
-from .mlp import PolyNormFF, SwiGLU
+from .delta_rule import GatedDeltaRule
+from .mlp import DenseFF, PolyNormFF, SwiGLU
 from .moe import RoutedMoE, TableMoE
 from .parallel import ParallelMixers
+from .sink_attention import SinkWindowAttention
+from .sinusoid import SinusoidalPositions
 from .state_space import ScalarDecayStateSpace
 from .model import Layer, Model, tensor_specs_of
 from .norm import RMSNorm
@@ -34,6 +37,10 @@ register("block", "sandwich_norm", SandwichNormBlock)
 register("mixer", "parallel_mixers", ParallelMixers)
 register("mixer", "scalar_decay_state_space", ScalarDecayStateSpace)
 register("feed_forward", "routed_moe", RoutedMoE)
+register("mixer", "sink_window_attention", SinkWindowAttention)
+register("mixer", "gated_delta_rule", GatedDeltaRule)
+register("feed_forward", "dense_ff", DenseFF)
+register("position_encoding", "sinusoidal", SinusoidalPositions)
 
 __all__ = ["ATTENTION_WORK", "AttentionWork", "GQAAttention", "Block", "BuildEnv", "CacheNeed", "FeedForward",
            "KVRequest", "LayerCache", "Mixer", "Norm", "Part", "PositionEncoding", "StateRequest", "StepPlanner", "PreNormBlock", "LMHead",
@@ -42,4 +49,4 @@ __all__ = ["ATTENTION_WORK", "AttentionWork", "GQAAttention", "Block", "BuildEnv
            "register_norm", "register_position_encoding", "RotaryEncoding", "rotary_inv_freq",
            "LayerSpec", "ModelSpec", "PartSpec", "RunStep", "TokenFilter", "DepthAveragedBlock", "CausalShortConv",
            "LatentAttention", "DecayLinearAttention", "PolyNormFF", "TableMoE", "SandwichNormBlock", "ParallelMixers",
-           "ScalarDecayStateSpace", "RoutedMoE"]
+           "ScalarDecayStateSpace", "RoutedMoE", "SinkWindowAttention", "GatedDeltaRule", "DenseFF", "SinusoidalPositions"]

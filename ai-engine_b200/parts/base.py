@@ -31,7 +31,9 @@ class KVRequest:
     kv_heads: int
     head_dim: int
     window: int = 0
-    planes: int = 2      # 2: keys and values; 1: one vector per token and kv head (a compressed cache)
+    planes: int = 2      # 2: keys and values; 1: one vector per token and kv head (a compressed cache, or a key and
+    #                      a value of another size side by side in one row)
+    keep_first: int = 0  # with a window: the first `keep_first` keys stay readable for every later query
 
 
 @dataclass(frozen=True)

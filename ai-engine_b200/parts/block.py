@@ -15,19 +15,52 @@ from .base import Block
 
 
 class PreNormBlock(Block):
+    """x = x + mixer(norm(x)); x = x + ffn(norm(x)).  The feed-forward with its norm is optional.
+
+    With the tensor `input_mix` [hidden, 2 hidden], the block first replaces the stream by a projection of the
+    stream and the embedding's output side by side, x <- W [x ; x0] (a layer that opens a pass over a group of
+    layers which is run several times: every pass starts from the running stream and the embedding together).  The
+    projection reads both in the compute dtype and writes the new float32 stream."""
+
     roles = {"mixer_norm": "norm", "mixer": "mixer", "ffn_norm": "norm", "ffn": "feed_forward"}
+    optional_roles = ("ffn_norm", "ffn")
 
     def __init__(self, spec, env, parts):
         super().__init__(spec, env)
         self.mixer_norm, self.mixer = parts["mixer_norm"], parts["mixer"]
-        self.ffn_norm, self.ffn = parts["ffn_norm"], parts["ffn"]
+        self.ffn_norm, self.ffn = parts.get("ffn_norm"), parts.get("ffn")
+        if (self.ffn is None) != (self.ffn_norm is None):
+            raise ValueError("pre-norm block: a feed-forward comes with its norm")
+        self.hidden = env.hidden_size
+        self.w_mix = None
+        self.needs_embedding_output = "input_mix" in spec.tensors
+
+    def tensor_specs(self):
+        name = self.spec.tensors.get("input_mix")
+        return [TensorSpec(name, (self.hidden, 2 * self.hidden))] if name else []
+
+    def load(self, source):
+        name = self.spec.tensors.get("input_mix")
+        if name:
+            self.w_mix = source.get(name)
+
+    def weight_bytes(self):
+        return self.w_mix.numel() * self.w_mix.element_size() if self.w_mix is not None else 0
+
+    def flops(self, tokens, keys=0.0):
+        return 4.0 * tokens * self.hidden * self.hidden if self.w_mix is not None else 0.0
 
     def forward(self, x, pending, ctx, caches):
+        if self.w_mix is not None:
+            both = ops.join_streams(x, pending, ctx.embedding_output, self.env.dtype)
+            x, pending = ops.linear(both, self.w_mix, torch.float32, ctx.err), None
         h = self.mixer_norm.forward(x, pending)
         if self.mixer.adds_in_place:      # a large step's output projection adds to the stream itself: a is None then
             a = self.mixer.forward(h, ctx, caches.get("mixer"), add_to=x)
         else:
             a = self.mixer.forward(h, ctx, caches.get("mixer"))
+        if self.ffn is None:
+            return x, a
         h = self.ffn_norm.forward(x, a)
         if self.ffn.adds_in_place:
             return x, self.ffn.forward(h, ctx, add_to=x)

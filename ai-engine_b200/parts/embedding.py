@@ -33,13 +33,14 @@ class TokenEmbedding(Part):
 
 class LMHead(Part):
     """params: vocab_size, hidden_size, alternatives, stored, softcap (0 or absent: none; c > 0: the logits
-    become c * tanh(logits / c)).  tensors: weight [vocab, hidden] (the embedding's name when tied).
+    become c * tanh(logits / c)), scale (absent or 1: none; the logits are multiplied by it, before a softcap).  tensors: weight [vocab, hidden] (the embedding's name when tied).
     forward(h [N, hidden]) -> float32 logits [N, vocab]."""
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
         self.vocab, self.hidden = int(spec.params["vocab_size"]), int(spec.params["hidden_size"])
         self.softcap = float(spec.params.get("softcap") or 0.0)
+        self.scale = float(spec.params.get("scale") or 1.0)
         if self.softcap < 0:
             raise ValueError(f"head: softcap must be positive, got {self.softcap}")
         self.weight = None
@@ -60,4 +61,6 @@ class LMHead(Part):
 
     def forward(self, h, err=None):
         logits = ops.linear(h, self.weight, torch.float32, err)
+        if self.scale != 1.0:
+            logits = ops.scale_(logits, self.scale)
         return ops.softcap(logits, self.softcap) if self.softcap else logits

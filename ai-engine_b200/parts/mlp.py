@@ -98,3 +98,41 @@ class PolyNormFF(FeedForward):
         if add_to is not None and ops.linear_add(add_to, a, self.w_down):
             return None
         return ops.linear_parts(a, self.w_down, ctx.err)
+
+
+class DenseFF(FeedForward):
+    """down(act(up(x))) without a gate.  params: hidden_size, intermediate_size, activation (relu_squared, the
+    default; relu, silu, gelu_tanh).  tensors: up [F, hidden], down [hidden, F].  The activation is worked out in
+    float32 from the product's output."""
+
+    adds_in_place = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden, self.inter = int(spec.params["hidden_size"]), int(spec.params["intermediate_size"])
+        self.activation = spec.params.get("activation") or "relu_squared"
+        if self.activation not in ops.PLAIN_ACTIVATIONS:
+            raise ValueError(f"feed-forward: activation `{self.activation}` is not known "
+                             f"({', '.join(ops.PLAIN_ACTIVATIONS)})")
+        self.w_up = self.w_down = None
+
+    def tensor_specs(self):
+        t = self.spec.tensors
+        return [TensorSpec(t["up"], (self.inter, self.hidden)), TensorSpec(t["down"], (self.hidden, self.inter))]
+
+    def load(self, source):
+        t = self.spec.tensors
+        self.w_up, self.w_down = source.get(t["up"]), source.get(t["down"])
+
+    def weight_bytes(self):
+        return sum(w.numel() * w.element_size() for w in (self.w_up, self.w_down))
+
+    def flops(self, tokens, keys=0.0):
+        return 2.0 * tokens * 2 * self.inter * self.hidden
+
+    def forward(self, h, ctx, add_to=None):
+        err = ctx.err if ctx is not None else None
+        a = ops.linear_activated(h, self.w_up, self.activation, err)
+        if add_to is not None and ops.linear_add(add_to, a, self.w_down):
+            return None
+        return ops.linear_parts(a, self.w_down, err)

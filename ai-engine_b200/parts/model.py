@@ -64,6 +64,7 @@ class Model:
                                                   self.order[rs.cache_from].cache_from is None):
                 raise ValueError(f"run order entry {i}: cache_from must name an earlier entry "
                                  f"that has a cache of its own")
+        self.keeps_embedding_output = any(getattr(l.block, "needs_embedding_output", False) for l in self.layers)
         self.loaded = False
 
     # -- parts and tensors ---------------------------------------------------
@@ -137,6 +138,7 @@ class Model:
         total = self.lm_head.flops(logit_rows) + self.final_norm.flops(logit_rows)
         for rs in self.order:
             total += sum(p.flops(tokens, keys) for p in self.layers[rs.layer].parts.values())
+            total += self.layers[rs.layer].block.flops(tokens, keys)
         return total
 
     def step_weight_bytes(self) -> int:
@@ -144,16 +146,29 @@ class Model:
         total = self.lm_head.weight_bytes() + self.final_norm.weight_bytes()
         for rs in self.order:
             total += sum(p.weight_bytes() for p in self.layers[rs.layer].parts.values())
+            total += self.layers[rs.layer].block.weight_bytes()
         return total
 
     # -- the forward pass of one step -----------------------------------------
-    def forward(self, ctx, cache) -> torch.Tensor:
+    def forward(self, ctx, cache, streams: Optional[list] = None) -> torch.Tensor:
+        """`streams`: a list that receives the residual stream [T, hidden] (float32, a copy) behind every entry
+        of the run order, for looking at a model layer by layer."""
         x = self.embedding.forward(ctx)
         for pe in self.env.position_encodings.values():
             pe.add_to(x, ctx)
+        if self.keeps_embedding_output:
+            # a block that reads the embedding's output later finds it on the step; layers before it write into the
+            # stream in place, so it is copied unless that block comes first and makes a stream of its own
+            first = self.layers[self.order[0].layer].block
+            ctx.embedding_output = x if getattr(first, "needs_embedding_output", False) else x.clone()
         pending = None
         for i, rs in enumerate(self.order):
             x, pending = self.layers[rs.layer].block.forward(x, pending, ctx, cache.layer_cache(i, ctx))
+            if streams is not None:
+                full = x.clone()
+                if pending is not None:
+                    full += pending.float().sum(dim=0) if pending.dim() == 3 else pending.float()
+                streams.append(full)
         if ctx.num_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         h = self.final_norm.forward(x, pending, rows=ctx.logit_rows, write_back=False)
