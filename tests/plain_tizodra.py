@@ -80,12 +80,12 @@ def sink_attention(h, w: Dict[str, torch.Tensor], m: dict, eps: float, first_pos
         g = a // (H // G)
         for t in range(T):
             i = first_position + t
-            js = [j for j in range(T) if visible(i, first_position + j, size, keep)]
-            s = torch.stack([(q[t, a] @ k[j, g]) * m["scale"] * w["temp"][a] - slopes[a] * (t - j) for j in js])
+            js = torch.tensor([j for j in range(T) if visible(i, first_position + j, size, keep)], dtype=torch.long)
+            s = (k[js, g] @ q[t, a]) * m["scale"] * w["temp"][a] - slopes[a] * (t - js).to(h.dtype)
             top = torch.maximum(s.max(), w["sink"][a])
             p = torch.exp(s - top)
             denom = p.sum() + torch.exp(w["sink"][a] - top)           # the sink: a weight without a value
-            out[t, a] = (p[:, None] * torch.stack([v[j, g] for j in js])).sum(dim=0) / denom
+            out[t, a] = (p[:, None] * v[js, g]).sum(dim=0) / denom
     out = out * gate[:, :, None]
     return out.reshape(T, H * e) @ w["o"].T
 
