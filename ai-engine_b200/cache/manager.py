@@ -175,6 +175,17 @@ class PagedCache:
         es = torch.empty((), dtype=self.dtype).element_size()
         return sum(g.bytes_per_token for g in self.groups) * es
 
+    def kv_bytes_read(self, cached_tokens: float) -> float:
+        """Bytes of keys and values that one token reads of a request with `cached_tokens` tokens: every group's
+        rows, a group with a window no more than the window and its kept first keys."""
+        es = torch.empty((), dtype=self.dtype).element_size()
+        total = 0.0
+        for g in self.groups:
+            r = g.request
+            seen = min(cached_tokens, r.window + r.keep_first) if r.window > 0 else cached_tokens
+            total += g.bytes_per_token * seen
+        return total * es
+
     def stats(self) -> dict:
         return {f"group{g}": dict(pages=grp.num_pages, in_use=self.book.pages_in_use(g),
                                   high_water=self.book.high_water(g),

@@ -95,6 +95,21 @@ def zupitar_shape(width, layers=8):
     return dict(architecture="Zupitar", vocab=32000, width=width, norm=dict(eps=1e-5), logit_softcap=30.0, layers=out)
 
 
+def tizodra_shape(width, layers=8):
+    """A Tizodra configuration with layers of the sizes real models of its kind have: attention heads of 128 for keys
+    and values (a quarter of them key/value heads) under a window of 1,024 keys that keeps the first four; delta-rule
+    heads of 128 x 128 (half as many query/key heads, four taps); a feed-forward of 3 x width.  The pattern (delta,
+    attention, attention) repeats; the first three layers run twice, so `layers` layer runs hold layers - 3 layers."""
+    H = width // 128
+    att = dict(type="attention", mixer=dict(heads=H, kv_heads=max(1, H // 4), dim=128, vdim=128, scale=128 ** -0.5,
+                                            mask=dict(size=1024, keep_first=4)))
+    dlt = dict(type="delta", mixer=dict(heads=H, kv_heads=max(1, H // 2), dim=128, vdim=128, conv=4))
+    n = max(3, layers - 3)
+    out = [dict(dlt if i % 3 == 0 else att, mlp=dict(kind="dense", ff=3 * width)) for i in range(n)]
+    return dict(architecture="Tizodra", vocab=32000, width=width, norm=dict(eps=1e-5), logit_scale=1.0,
+                loop=dict(start=0, stop=3, times=2), layers=out)
+
+
 def llama_like(width, layers=8):
     """The closest existing model at equal size: the same width, layers, heads of 128 (a quarter of them kv heads)
     and a feed-forward of 3 x width, which is what a Pifutar token uses (4 experts of width / 2 + the shared one)."""
@@ -215,7 +230,9 @@ def time_decode(torch, aie, model, batch, prompt_len, steps, warmup, ctx_cap, bl
     ctx_tokens = batch * (prompt_len + warmup + steps * blocks / 2.0)
     # weights once, every cached key and value once, and every request's state read and written
     state_bytes = sum(t[0].numel() * t.element_size() for t in cache.state_tensors()) if hasattr(cache, "state_tensors") else 0
-    bytes_step = model.step_weight_bytes() + cache.kv_bytes_per_token() * ctx_tokens + 2 * state_bytes * batch
+    # (a group with a window reads no more than the window and its kept first keys of a request)
+    kv_bytes = cache.kv_bytes_read(ctx_tokens / batch) * batch if hasattr(cache, "kv_bytes_read") else cache.kv_bytes_per_token() * ctx_tokens
+    bytes_step = model.step_weight_bytes() + kv_bytes + 2 * state_bytes * batch
     del cache, runner
     torch.cuda.empty_cache()
     return dict(ms=ms, ms_min=min(per_block), ms_max=max(per_block), blocks=blocks, tok_s=batch * 1000.0 / ms,
@@ -635,10 +652,10 @@ def main():
                     help="time one part only and print its numbers (for profiling)")
     ap.add_argument("--profile", action="store_true",
                     help="CUDA-event time, bytes, flops and roofline fraction per class of kernel (eager launches)")
-    ap.add_argument("--shape", choices=["8b", "1b", "3b"] + [f"{m}-{w}" for m in ("pifutar", "zupitar", "llama") for w in WIDTHS],
+    ap.add_argument("--shape", choices=["8b", "1b", "3b"] + [f"{m}-{w}" for m in ("pifutar", "zupitar", "tizodra", "llama") for w in WIDTHS],
                     default="8b",
                     help="layer sizes for --profile and --only decode|prefill (the headline run is always the 8B shape); "
-                         "pifutar-1k|2k|4k, zupitar-1k|2k|4k: those designs at that width, llama-1k|2k|4k: Llama at equal size beside them "
+                         "pifutar-1k|2k|4k, zupitar-1k|2k|4k, tizodra-1k|2k|4k: those designs at that width, llama-1k|2k|4k: Llama at equal size beside them "
                          "(8 layers unless --layers says otherwise)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="cached tokens per request for --profile / --only decode")
     ap.add_argument("--skip-workloads", action="store_true", help="leave the 1B and 3B serving workloads out of `points`")
@@ -685,7 +702,7 @@ def main():
     if "-" in a.shape and (a.profile or a.only):
         family, w = a.shape.split("-")
         layers = a.layers if a.layers != LLAMA3_8B["num_hidden_layers"] else 8
-        cfg = dict(pifutar=pifutar_shape, zupitar=zupitar_shape, llama=llama_like)[family](WIDTHS[w], layers)
+        cfg = dict(pifutar=pifutar_shape, zupitar=zupitar_shape, tizodra=tizodra_shape, llama=llama_like)[family](WIDTHS[w], layers)
     else:
         cfg = dict({"8b": LLAMA3_8B, "1b": LLAMA32_1B, "3b": LLAMA32_3B}.get(a.shape, LLAMA3_8B) if (a.profile or a.only) else LLAMA3_8B)
         if a.layers != LLAMA3_8B["num_hidden_layers"] or a.shape == "8b":
