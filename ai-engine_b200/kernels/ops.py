@@ -1107,13 +1107,18 @@ def sink_attn_prepare(proj: torch.Tensor, bias: Optional[torch.Tensor], pages: t
     return q, gate
 
 
+SINK_FAST_SIZES = (32, 64, 128)      # key and value sizes of the tensor-core kernels of sink_attention
+
+
 def sink_attention(q: torch.Tensor, pages: torch.Tensor, gate: Optional[torch.Tensor], temp: Optional[torch.Tensor],
                    slope: Optional[torch.Tensor], sink: Optional[torch.Tensor], ctx, work, block_table: torch.Tensor,
                    e: int, scale: float, window: int, keep_first: int) -> torch.Tensor:
     """Attention of a step's query tokens over cache rows [k (d) | v (e)]:
     s(i, j) = (q_i . k_j) * scale * temp[h] - slope[h] * (i - j) over the keys j <= i with i - j < window or
     j < keep_first (window 0: all); softmax whose denominator also holds exp(sink[h]); times gate[i, h].
-    q [T, H, d]; gate [T, H], temp, slope, sink [H] float32 or None.  Returns [T, H, e] in q's dtype."""
+    q [T, H, d]; gate [T, H], temp, slope, sink [H] float32 or None.  Returns [T, H, e] in q's dtype.
+    bfloat16 with key and value sizes of 32, 64 or 128: lone tokens take the split-KV kernel, portions of prompts
+    the tiled tensor-core kernel (`work`: the attention work lists); everything else takes the plain kernel."""
     _dev(q, pages, gate, temp, slope, sink, block_table)
     T, H, d = q.shape
     G = pages.shape[1]
@@ -1129,6 +1134,33 @@ def sink_attention(q: torch.Tensor, pages: torch.Tensor, gate: Optional[torch.Te
         rows = (cl + ql).clip(max=float(window + keep_first) + ql) if window > 0 else cl + ql
         cost = (float(rows.sum()) * G * (d + e) * pages.element_size() + _nb(q, out),
                 2.0 * float((ql * seen).sum()) * H * (d + e))
+    if q.dtype == torch.bfloat16 and d in SINK_FAST_SIZES and e in SINK_FAST_SIZES:
+        fast = library("sink_attention_tc.cu")
+        common = (_p(block_table), c_int(block_table.shape[1]), c_int(pages.shape[0]), c_int(pages.shape[2]),
+                  c_int(H), c_int(G), c_int(d), c_int(e), c_int(window), c_int(keep_first), c_float(scale))
+        if work.n_decode:
+            n = work.n_decode
+            keys = work.max_decode_len if window <= 0 else min(window + keep_first, work.max_decode_len)
+            S = min(decode_splits(n, G, H // G, keys), 64)
+            part_o = part_lse = None
+            if S > 1:
+                part_o = torch.empty((n, H, S, e), dtype=torch.float32, device=q.device)
+                part_lse = torch.empty((n, H, S), dtype=torch.float32, device=q.device)
+            share = float(n) / T
+            with region("sink_attention_decode", cost[0] * share, cost[1] * share):
+                check(fast.aie_sink_attention_decode(_p(q), _p(pages), _p(out), _p(part_o), _p(part_lse), _p(gate),
+                                                     _p(temp), _p(slope), _p(sink), _p(work.decode_tokens), c_int(n),
+                                                     _p(ctx.positions), _p(ctx.token_req), *common, c_int(S),
+                                                     _p(ctx.err), _stream()), "sink_attention_decode")
+        if work.n_decode < ctx.R:
+            tiles = work.prefill_tiles
+            share = 1.0 - float(work.n_decode) / T
+            with region("sink_attention_prefill", cost[0] * share, cost[1] * share):
+                check(fast.aie_sink_attention_prefill(_p(q), _p(pages), _p(out), _p(gate), _p(temp), _p(slope), _p(sink),
+                                                      _p(tiles), c_int(tiles.shape[0]), _p(ctx.q_start), _p(ctx.q_len),
+                                                      _p(ctx.ctx_len), *common, _p(ctx.err), _stream()),
+                      "sink_attention_prefill")
+        return out
     lib = library("sink_attention.cu")
     with region("sink_attention_plain", *cost):
         check(lib.aie_sink_attention_plain(_p(q), _p(pages), _p(out), c_int(dtype_code(q)), _p(gate), _p(temp), _p(slope),

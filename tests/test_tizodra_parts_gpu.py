@@ -123,14 +123,15 @@ def test_attention_three_requests_in_unequal_portions(dtype, shape):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("sizes", [(32, 16), (32, 64)])        # the second pair takes the tensor-core kernels in bfloat16
 @pytest.mark.parametrize("window,keep,page", [(40, 3, 8), (96, 8, 16), (130, 1, 32), (0, 0, 8)])
-def test_attention_planted_keys_at_every_edge(dtype, window, keep, page):
+def test_attention_planted_keys_at_every_edge(dtype, window, keep, page, sizes):
     """Pairs of tokens with a strong input that the later one's query and the earlier one's key read alike, so that
     the later one's weight goes to the earlier one when it reads it: just inside the window and just outside, the last kept token and the first one behind the kept run, at
     a page's first and last place, and 250 tokens back.  A window one key off, a lost page or a kept token that is
     not read moves those rows by the whole output."""
     hidden, n = 128, 300
-    m = dict(heads=4, kv_heads=4, dim=32, vdim=16, scale=0.05)
+    m = dict(heads=4, kv_heads=4, dim=sizes[0], vdim=sizes[1], scale=0.05)
     if window:
         m["mask"] = dict(size=window, keep_first=keep)
     gen = torch.Generator().manual_seed(50 + window)
