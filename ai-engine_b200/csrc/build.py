@@ -29,7 +29,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a",
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden"]
 
 CUDA_SOURCES = ["elementwise.cu", "rope_kv.cu", "attention_plain.cu", "gemm_f32.cu",
-                "sampling.cu", "sequence_ops.cu", "latent_attention.cu", "latent_attention_tc.cu", "linear_recurrence.cu", "state_space_chunked.cu", "sink_attention.cu", "sink_attention_tc.cu", "delta_rule.cu", "attention_fast.cu", "attention_decode_noalloc.cu", "gemm_tc.cu", "attention_prefill_tc.cu"]
+                "sampling.cu", "sequence_ops.cu", "latent_attention.cu", "latent_attention_tc.cu", "linear_recurrence.cu", "state_space_chunked.cu", "sink_attention.cu", "sink_attention_tc.cu", "delta_rule.cu", "delta_rule_chunked.cu", "attention_fast.cu", "attention_decode_noalloc.cu", "gemm_tc.cu", "attention_prefill_tc.cu"]
 
 
 class BuildError(RuntimeError):

@@ -27,7 +27,7 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
                   const float* __restrict__ a_log, const float* __restrict__ dt_bias, float q_scale, float unit_eps,
                   float* __restrict__ state, float* __restrict__ out, const int* __restrict__ q_start,
                   const int* __restrict__ q_len, const int* __restrict__ slots, const int* __restrict__ live,
-                  int H, int G, int d, int e, int max_seqs, unsigned* err) {
+                  int H, int G, int d, int e, int max_seqs, int max_len, unsigned* err) {
     extern __shared__ __align__(16) float sm[];
     float* k_s = sm;                                   // [TOKENS][d]
     float* q_s = k_s + DR_TOKENS * d;                  // [TOKENS][d]
@@ -47,6 +47,7 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
         return;
     }
     const int t0 = q_start[r], n = q_len[r];
+    if (max_len > 0 && n > max_len) return;            // longer portions went to the chunked kernel
     const int kh = h / (H / G);
     float* S = state + ((size_t)slot * H + h) * d * e;
     float s[RPT];
@@ -138,7 +139,7 @@ extern "C" int aie_delta_rule(const float* q, const float* k, const float* v, in
                               const float* a_raw, int lda, const float* a_log, const float* dt_bias, float q_scale,
                               float unit_eps, float* state, float* out, const int* q_start, const int* q_len,
                               const int* slots, const int* live, int R, int H, int G, int d, int e, int max_seqs,
-                              unsigned* err, cudaStream_t stream) {
+                              int max_len, unsigned* err, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G || d <= 0 || d > 256 || e <= 0 || H > 65535) return AIE_UNSUPPORTED;
     const size_t smem = (size_t)(2 * DR_TOKENS * d + DR_TOKENS * DR_COLS + 3 * DR_TOKENS) * sizeof(float);
@@ -146,7 +147,7 @@ extern "C" int aie_delta_rule(const float* q, const float* k, const float* v, in
 #define AIE_DR(RPT)                                                                                                \
     delta_rule_kernel<RPT><<<grid, DR_THREADS, smem, stream>>>(q, k, v, ld, b_raw, ldb, a_raw, lda, a_log, dt_bias, \
                                                                q_scale, unit_eps, state, out, q_start, q_len, slots, \
-                                                               live, H, G, d, e, max_seqs, err)
+                                                               live, H, G, d, e, max_seqs, max_len, err)
     if (d <= 32) AIE_DR(4);
     else if (d <= 64) AIE_DR(8);
     else if (d <= 128) AIE_DR(16);

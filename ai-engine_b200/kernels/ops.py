@@ -1172,14 +1172,21 @@ def sink_attention(q: torch.Tensor, pages: torch.Tensor, gate: Optional[torch.Te
     return out
 
 
+DELTA_MIN_TOKENS = 32    # portions from this length on take the chunked delta-rule kernel (bfloat16 mode)
+DELTA_CHUNK = 64         # its chunk
+
+
 def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, b_raw: torch.Tensor, a_raw: torch.Tensor,
                a_log: torch.Tensor, dt_bias: torch.Tensor, q_scale: float, unit_eps: float, state: torch.Tensor, ctx,
-               H: int, G: int, d: int, e: int) -> torch.Tensor:
+               H: int, G: int, d: int, e: int, chunked: bool = False) -> torch.Tensor:
     """The gated delta rule over a step's tokens, the state [max_seqs, H, d, e] float32 read and left in each
     request's slot:  q, k made unit vectors per head (x / sqrt(|x|^2 + unit_eps), q times q_scale);
     beta = sigmoid(b_raw); g = exp(-exp(a_log) softplus(a_raw + dt_bias));  S <- g S;  u = beta (v - S^T k);
     S <- S + k u^T;  o = S^T q.  q, k [T, G d] and v [T, H e] are float32 views with one row stride; b_raw, a_raw
-    [T, H] float32 views (rows any stride); head h reads q/k head h / (H / G).  Returns o [T, H, e] float32."""
+    [T, H] float32 views (rows any stride); head h reads q/k head h / (H / G).  chunked: portions of
+    DELTA_MIN_TOKENS tokens or more take the chunked tensor-core kernel, whose products see 16 bits of mantissa
+    (a state of up to 128 rows); everything else, and all of a float32 engine, goes token by token in float32.
+    Returns o [T, H, e] float32."""
     _dev(a_log, dt_bias, state)
     T, ld = q.shape[0], q.stride(0)
     if (q.dtype != torch.float32 or k.dtype != torch.float32 or v.dtype != torch.float32 or k.stride(0) != ld
@@ -1188,11 +1195,27 @@ def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, b_raw: torch.T
             or state.shape[1:] != (H, d, e) or state.dtype != torch.float32 or H % G or d > 256):
         raise KernelError("delta_rule: shapes or dtypes do not fit")
     out = torch.empty((T, H, e), dtype=torch.float32, device=q.device)
+    max_len = 0
+    if (chunked and d <= 128 and ctx.max_q_len >= DELTA_MIN_TOKENS
+            and not os.environ.get("AI_ENGINE_B200_NO_CHUNKED_SCAN")):      # the switch is for measurement
+        lib = library("delta_rule_chunked.cu")
+        Q = DELTA_CHUNK
+        with region("delta_rule_chunked", _nb(out) + T * (2 * G * d + H * e) * 4 + 2 * ctx.R * H * d * e * 4,
+                    2.0 * T * H * (Q * d + Q * e + 3 * d * e)):
+            check(lib.aie_delta_rule_chunked(_p(q), _p(k), _p(v), c_int(ld), _p(b_raw), c_int(b_raw.stride(0)), _p(a_raw),
+                                             c_int(a_raw.stride(0)), _p(a_log), _p(dt_bias), c_float(q_scale),
+                                             c_float(unit_eps), _p(state), _p(out), _p(ctx.q_start), _p(ctx.q_len),
+                                             _p(ctx.slots), _p(ctx.live), c_int(ctx.R), c_int(H), c_int(G), c_int(d),
+                                             c_int(e), c_int(state.shape[0]), c_int(DELTA_MIN_TOKENS), _p(ctx.err),
+                                             _stream()), "delta_rule_chunked")
+        if int(ctx.h_q_len.min()) >= DELTA_MIN_TOKENS:
+            return out
+        max_len = DELTA_MIN_TOKENS - 1              # the shorter portions and single tokens of the same step
     lib = library("delta_rule.cu")
     with region("delta_rule", _nb(out) + T * (2 * G * d + H * e) * 4 + 2 * ctx.R * H * d * e * 4, 6.0 * T * H * d * e):
         check(lib.aie_delta_rule(_p(q), _p(k), _p(v), c_int(ld), _p(b_raw), c_int(b_raw.stride(0)), _p(a_raw),
                                  c_int(a_raw.stride(0)), _p(a_log), _p(dt_bias), c_float(q_scale), c_float(unit_eps),
                                  _p(state), _p(out), _p(ctx.q_start), _p(ctx.q_len), _p(ctx.slots), _p(ctx.live),
                                  c_int(ctx.R), c_int(H), c_int(G), c_int(d), c_int(e), c_int(state.shape[0]),
-                                 _p(ctx.err), _stream()), "delta_rule")
+                                 c_int(max_len), _p(ctx.err), _stream()), "delta_rule")
     return out

@@ -79,7 +79,8 @@ class GatedDeltaRule(Mixer):
         qkv = ops.causal_conv(proj[:, :C], self.w_conv, None, cache.state["tail"], ctx, torch.float32, activation="silu")
         o = ops.delta_rule(qkv[:, :Gd], qkv[:, Gd:2 * Gd], qkv[:, 2 * Gd:], proj[:, C + He:C + He + self.H],
                            proj[:, C + He + self.H:C + He + 2 * self.H], self.a_log, self.dt_bias,
-                           float(self.d) ** -0.5, self.unit_eps, cache.state["S"], ctx, self.H, self.G, self.d, self.e)
+                           float(self.d) ** -0.5, self.unit_eps, cache.state["S"], ctx, self.H, self.G, self.d, self.e,
+                           chunked=self.env.dtype != torch.float32)
         y = ops.head_norm_gate(o, proj[:, C:C + He], self.norm_w, self.eps, self.env.dtype)
         if add_to is not None and ops.linear_add(add_to, y, self.w_o):
             return None

@@ -221,3 +221,42 @@ def test_delta_rule_state_against_the_oracle():
     S = lc.state["S"][slot].double().cpu()
     for a in range(m["heads"]):
         assert float((S[a] - keep[a]).abs().max()) < 1e-5
+
+
+@pytest.mark.parametrize("sizes", [(4, 2, 24, 20), (2, 1, 64, 64), (2, 2, 128, 72), (3, 1, 40, 100), (1, 1, 32, 32),
+                                   (148, 4, 16, 40)])
+def test_delta_rule_in_chunks_against_token_by_token(sizes):
+    """The chunked kernel and the token-by-token kernel on the same float32 inputs, from the same non-zero state,
+    agree to float32 rounding times the chunk's length: a portion of several chunks with a ragged end, a portion of
+    one short chunk, and beside them a single token and a portion too short for chunks, all in one step.  Decays
+    from near one to strong, corrections from weak to full."""
+    from ai_engine_b200.kernels import ops
+    H, G, d, e = sizes
+    gen = torch.Generator().manual_seed(H * 1000 + d)
+    part, _ = delta_part(dict(heads=H, kv_heads=G, dim=d, vdim=e, conv=2), 16, 1e-5, "bfloat16", gen)
+    rig = Rig(part, torch.bfloat16, page=8, pages=64, max_seqs=4)
+    lens = [150, 1, 40, 31] if H < 100 else [70, 1]
+    slots = [rig.admit() for _ in lens]
+    portions = list(zip(slots, lens))
+    ctx, lc = rig.step(portions)
+    T = sum(lens)
+    qkv = (torch.randn(T, 2 * G * d + H * e, generator=gen) * 1.5).to(DEV)
+    b_raw = (torch.randn(T, H, generator=gen) * 2.0).to(DEV)
+    a_raw = (torch.randn(T, H, generator=gen) * 3.0).to(DEV)
+    a_log = (torch.randn(H, generator=gen) * 0.7 - 0.5).to(DEV)
+    dt_bias = (torch.randn(H, generator=gen) * 0.5 - 1.0).to(DEV)
+    S0 = (torch.randn(lc.state["S"].shape, generator=gen) * 0.5).to(DEV)
+    res = []
+    for chunked in (False, True):
+        S = S0.clone()
+        o = ops.delta_rule(qkv[:, :G * d], qkv[:, G * d:2 * G * d], qkv[:, 2 * G * d:], b_raw, a_raw, a_log, dt_bias,
+                           d ** -0.5, 1e-6, S, ctx, H, G, d, e, chunked=chunked)
+        torch.cuda.synchronize()
+        res.append((o.double().cpu(), S.double().cpu()))
+    assert int(rig.err.item()) == 0
+    (o0, s0), (o1, s1) = res
+    for what, a, b in (("output", o0, o1), ("state", s0, s1)):
+        spread = float(a.std())
+        diff = (a - b).abs()
+        assert float(diff.max()) <= 3e-4 * spread, f"{what} {sizes}: {float(diff.max()):.3e} of spread {spread:.3e} at {int(diff.flatten().argmax())}"
+    assert float((s1 - S0.double().cpu()).abs().max()) > 1e-3       # the states did move
