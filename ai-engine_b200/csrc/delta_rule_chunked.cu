@@ -37,21 +37,26 @@ __device__ __forceinline__ void dc_split(float v, bf16* hi, bf16* lo) {
     *lo = __float2bfloat16_rn(v - __bfloat162float(h));
 }
 
-// acc += (aH + aL) (bH + bL) without the lo lo term, over `steps` tiles of 16 along the inner dimension
+// acc += (aH + aL) (bH + bL) without the lo lo term, over `steps` tiles of 16 along the inner dimension.  The three
+// products have an accumulator each, so that a warp has three independent chains of tensor-core instructions in flight.
 template <class FA, class FB>
 __device__ __forceinline__ void dc_mma3(FragC& acc, const bf16* aH, const bf16* aL, int lda, int a_step, const bf16* bH,
                                         const bf16* bL, int ldb, int b_step, int steps) {
+    FragC hl, lh;
+    wmma::fill_fragment(hl, 0.f);
+    wmma::fill_fragment(lh, 0.f);
     for (int k = 0; k < steps; ++k) {
         FA ah, al;
         FB bh, bl;
         wmma::load_matrix_sync(ah, aH + (size_t)k * a_step, lda);
         wmma::load_matrix_sync(bh, bH + (size_t)k * b_step, ldb);
-        wmma::mma_sync(acc, ah, bh, acc);
         wmma::load_matrix_sync(bl, bL + (size_t)k * b_step, ldb);
-        wmma::mma_sync(acc, ah, bl, acc);
         wmma::load_matrix_sync(al, aL + (size_t)k * a_step, lda);
-        wmma::mma_sync(acc, al, bh, acc);
+        wmma::mma_sync(acc, ah, bh, acc);
+        wmma::mma_sync(hl, ah, bl, hl);
+        wmma::mma_sync(lh, al, bh, lh);
     }
+    for (int x = 0; x < acc.num_elements; ++x) acc.x[x] += hl.x[x] + lh.x[x];
 }
 
 // which tile of the ten on and below the diagonal of a 4 x 4 grid
@@ -69,7 +74,7 @@ delta_rule_chunked_kernel(const float* __restrict__ qg, const float* __restrict_
                           const float* __restrict__ a_log, const float* __restrict__ dt_bias, float q_scale, float unit_eps,
                           float* __restrict__ state, float* __restrict__ out, const int* __restrict__ q_start,
                           const int* __restrict__ q_len, const int* __restrict__ slots, const int* __restrict__ live, int H,
-                          int G, int d, int e, int col_blocks, int max_slots, int min_len, unsigned* err) {
+                          int G, int d, int e, int col_blocks, int max_slots, int min_len, int vec4, unsigned* err) {
     extern __shared__ __align__(128) unsigned char dc_sm[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cb = blockIdx.x % col_blocks, h = (blockIdx.x / col_blocks) % H, r = blockIdx.x / (col_blocks * H);
@@ -97,9 +102,11 @@ delta_rule_chunked_kernel(const float* __restrict__ qg, const float* __restrict_
     bf16* UL = UH + DC_Q * LD;
     bf16* WH = UL + DC_Q * LD;                                    // [Q][DV] w * U
     bf16* WL = WH + DC_Q * LD;
-    float* G1 = reinterpret_cast<float*>(WL + DC_Q * LD);         // [Q][Q] K K^T, then the right-hand side and U [Q][DV]
-    float* G2 = G1 + DC_Q * FY;                                   // [Q][Q] Q K^T, then O [Q][DV]
-    float* Sf = G2 + DC_Q * FY;                                   // [NP][DV]
+    float* G1 = reinterpret_cast<float*>(WL + DC_Q * LD);         // [Q][Q] K K^T
+    float* G2 = G1 + DC_Q * FY;                                   // [Q][Q] Q K^T
+    float* R1 = G2 + DC_Q * FY;                                   // [Q][DV] K S_0, then the right-hand side
+    float* R2 = R1 + DC_Q * FD;                                   // [Q][DV] Q S_0, then O
+    float* Sf = R2 + DC_Q * FD;                                   // [NP][DV]
     float* Ad = Sf + NP * FD;                                     // [4][16][16] diagonal blocks of A
     float* Md = Ad + 4 * 256;                                     // [4][16][16] inverses of I + those
     float* la = Md + 4 * 256;                                     // [Q] running sums of log decays
@@ -124,17 +131,33 @@ delta_rule_chunked_kernel(const float* __restrict__ qg, const float* __restrict_
         constexpr int PERX = DC_Q * DV / DC_THREADS;
         float vv[PERX];                                // the chunk's values stay in registers until they are needed
         {
+            // a lane holds channels lane + 32 c; where a row of 128 channels can be read 16 bytes at a time, 4 lane + c
             float kv[ROWS][PER], qv[ROWS][PER];
+            const bool wide = PER == 4 && vec4;
+            if (wide) {
 #pragma unroll
-            for (int rr = 0; rr < ROWS; ++rr) {
-                const int t = warp + rr * DC_WARPS;
-#pragma unroll
-                for (int c = 0; c < PER; ++c) {
-                    const int n = lane + 32 * c;
-                    const bool ok = t < nt && n < d;
+                for (int rr = 0; rr < ROWS; ++rr) {
+                    const int t = warp + rr * DC_WARPS, n = 4 * lane;
+                    const bool ok = t < nt && n < d;               // d is a multiple of 4 here
                     const size_t at = (size_t)(a0 + t0 + t) * ld + (size_t)hq * d + n;
-                    kv[rr][c] = ok ? kg[at] : 0.f;
-                    qv[rr][c] = ok ? qg[at] : 0.f;
+                    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+                    const float4 kx = ok ? *reinterpret_cast<const float4*>(kg + at) : z;
+                    const float4 qx = ok ? *reinterpret_cast<const float4*>(qg + at) : z;
+                    kv[rr][0] = kx.x, kv[rr][1 % PER] = kx.y, kv[rr][2 % PER] = kx.z, kv[rr][3 % PER] = kx.w;
+                    qv[rr][0] = qx.x, qv[rr][1 % PER] = qx.y, qv[rr][2 % PER] = qx.z, qv[rr][3 % PER] = qx.w;
+                }
+            } else {
+#pragma unroll
+                for (int rr = 0; rr < ROWS; ++rr) {
+                    const int t = warp + rr * DC_WARPS;
+#pragma unroll
+                    for (int c = 0; c < PER; ++c) {
+                        const int n = lane + 32 * c;
+                        const bool ok = t < nt && n < d;
+                        const size_t at = (size_t)(a0 + t0 + t) * ld + (size_t)hq * d + n;
+                        kv[rr][c] = ok ? kg[at] : 0.f;
+                        qv[rr][c] = ok ? qg[at] : 0.f;
+                    }
                 }
             }
 #pragma unroll
@@ -166,7 +189,7 @@ delta_rule_chunked_kernel(const float* __restrict__ qg, const float* __restrict_
                 const float ik = rsqrtf(kk + unit_eps), iq = rsqrtf(qq + unit_eps) * q_scale;
 #pragma unroll
                 for (int c = 0; c < PER; ++c) {
-                    const int n = lane + 32 * c;
+                    const int n = wide ? 4 * lane + c : lane + 32 * c;
                     dc_split(kv[rr][c] * ik, KH + t * LN + n, KL + t * LN + n);
                     dc_split(qv[rr][c] * iq, QH + t * LN + n, QL + t * LN + n);
                 }
@@ -189,29 +212,54 @@ delta_rule_chunked_kernel(const float* __restrict__ qg, const float* __restrict_
             wv[2 * lane] = expf(end - (run - v1));
             wv[2 * lane + 1] = expf(end - run);
         }
-        // K K^T and Q K^T, the tiles on and below the diagonal
-        for (int job = warp; job < 20; job += DC_WARPS) {
-            int ti, tj;
-            dc_lower_tile(job < 10 ? job : job - 10, &ti, &tj);
-            const bf16* aH = (job < 10 ? KH : QH) + ti * 16 * LN;
-            const bf16* aL = (job < 10 ? KL : QL) + ti * 16 * LN;
+        // K K^T and Q K^T, the tiles on and below the diagonal; K S_0 and Q S_0
+        for (int job = warp; job < 20 + 8 * DT; job += DC_WARPS) {
             FragC acc;
             wmma::fill_fragment(acc, 0.f);
-            dc_mma3<FragA, FragBT>(acc, aH, aL, LN, 16, KH + tj * 16 * LN, KL + tj * 16 * LN, LN, 16, NP / 16);
-            wmma::store_matrix_sync((job < 10 ? G1 : G2) + ti * 16 * FY + tj * 16, acc, FY, wmma::mem_row_major);
+            if (job < 20) {
+                int ti, tj;
+                dc_lower_tile(job < 10 ? job : job - 10, &ti, &tj);
+                const bf16* aH = (job < 10 ? KH : QH) + ti * 16 * LN;
+                const bf16* aL = (job < 10 ? KL : QL) + ti * 16 * LN;
+                dc_mma3<FragA, FragBT>(acc, aH, aL, LN, 16, KH + tj * 16 * LN, KL + tj * 16 * LN, LN, 16, NP / 16);
+                wmma::store_matrix_sync((job < 10 ? G1 : G2) + ti * 16 * FY + tj * 16, acc, FY, wmma::mem_row_major);
+            } else {
+                const int jb = job - 20, which = jb / (4 * DT), ti = (jb / DT) % 4, tj = jb % DT;
+                dc_mma3<FragA, FragB>(acc, (which ? QH : KH) + ti * 16 * LN, (which ? QL : KL) + ti * 16 * LN, LN, 16,
+                                      SH + tj * 16, SL + tj * 16, LD, 16 * LD, NP / 16);
+                wmma::store_matrix_sync((which ? R2 : R1) + ti * 16 * FD + tj * 16, acc, FD, wmma::mem_row_major);
+            }
         }
         __syncthreads();
-        // -A and P on and below the diagonal, tile by tile (the tiles above it are never read)
-        for (int i = tid; i < 10 * 256; i += DC_THREADS) {
+        // -A and P on and below the diagonal, tile by tile and two neighbours a thread (the tiles above are never read)
+        for (int i = tid; i < 10 * 128; i += DC_THREADS) {
             int ti, tj;
-            dc_lower_tile(i >> 8, &ti, &tj);
-            const int el = i & 255, t = ti * 16 + (el >> 4), s = tj * 16 + (el & 15);
-            const float dec = expf(la[t] - la[s]);
-            const float a = s < t ? be[t] * dec * G1[t * FY + s] : 0.f;
-            const float p = s <= t ? dec * G2[t * FY + s] : 0.f;
-            dc_split(-a, NH + t * LQ + s, NL + t * LQ + s);
-            dc_split(p, PH + t * LQ + s, PL + t * LQ + s);
-            if (ti == tj) Ad[ti * 256 + el] = a;
+            dc_lower_tile(i >> 7, &ti, &tj);
+            const int pr = i & 127, tl = pr >> 3, sl = (pr & 7) * 2, t = ti * 16 + tl, s = tj * 16 + sl;
+            const float lt = la[t], bt = be[t];
+            const float2 ls = *reinterpret_cast<const float2*>(la + s);
+            const float2 g1 = *reinterpret_cast<const float2*>(G1 + t * FY + s);
+            const float2 g2 = *reinterpret_cast<const float2*>(G2 + t * FY + s);
+            const float d0 = __expf(lt - ls.x), d1 = __expf(lt - ls.y);
+            const float a0v = s < t ? bt * d0 * g1.x : 0.f, a1v = s + 1 < t ? bt * d1 * g1.y : 0.f;
+            const float p0 = s <= t ? d0 * g2.x : 0.f, p1 = s + 1 <= t ? d1 * g2.y : 0.f;
+            __nv_bfloat162 hi, lo;
+            dc_split(-a0v, &hi.x, &lo.x);
+            dc_split(-a1v, &hi.y, &lo.y);
+            *reinterpret_cast<__nv_bfloat162*>(NH + t * LQ + s) = hi;
+            *reinterpret_cast<__nv_bfloat162*>(NL + t * LQ + s) = lo;
+            dc_split(p0, &hi.x, &lo.x);
+            dc_split(p1, &hi.y, &lo.y);
+            *reinterpret_cast<__nv_bfloat162*>(PH + t * LQ + s) = hi;
+            *reinterpret_cast<__nv_bfloat162*>(PL + t * LQ + s) = lo;
+            if (ti == tj) *reinterpret_cast<float2*>(Ad + ti * 256 + tl * 16 + sl) = make_float2(a0v, a1v);
+        }
+        // the right-hand side beta (V - exp(l_t) K S_0), and the part of O that comes from the old state
+#pragma unroll
+        for (int it = 0; it < PERX; ++it) {
+            const int i = tid + it * DC_THREADS, t = i / DV, j = i % DV;
+            R1[t * FD + j] = be[t] * (vv[it] - ela[t] * R1[t * FD + j]);
+            R2[t * FD + j] *= ela[t];
         }
         __syncthreads();
         // the inverses of the diagonal blocks of I + A: a thread per column, forward substitution in registers
@@ -221,29 +269,16 @@ delta_rule_chunked_kernel(const float* __restrict__ qg, const float* __restrict_
             float m[16];
 #pragma unroll
             for (int t = 0; t < 16; ++t) {
-                float acc = t == c ? 1.f : 0.f;
+                float acc0 = t == c ? 1.f : 0.f, acc1 = 0.f;
 #pragma unroll
-                for (int s = 0; s < t; ++s) acc -= A[t * 16 + s] * m[s];
-                m[t] = acc;
-                Md[blk * 256 + t * 16 + c] = acc;
+                for (int s = 0; s + 1 < t; s += 2) {
+                    acc0 -= A[t * 16 + s] * m[s];
+                    acc1 -= A[t * 16 + s + 1] * m[s + 1];
+                }
+                if (t & 1) acc0 -= A[t * 16 + t - 1] * m[t - 1];
+                m[t] = acc0 + acc1;
+                Md[blk * 256 + t * 16 + c] = m[t];
             }
-        }
-        // K S_0 (into G1's place) and Q S_0 (into G2's)
-        for (int job = warp; job < 8 * DT; job += DC_WARPS) {
-            const int which = job / (4 * DT), ti = (job / DT) % 4, tj = job % DT;
-            FragC acc;
-            wmma::fill_fragment(acc, 0.f);
-            dc_mma3<FragA, FragB>(acc, (which ? QH : KH) + ti * 16 * LN, (which ? QL : KL) + ti * 16 * LN, LN, 16,
-                                  SH + tj * 16, SL + tj * 16, LD, 16 * LD, NP / 16);
-            wmma::store_matrix_sync((which ? G2 : G1) + ti * 16 * FY + tj * 16, acc, FY, wmma::mem_row_major);
-        }
-        __syncthreads();
-        // the right-hand side beta (V - exp(l_t) K S_0), and the part of O that comes from the old state
-#pragma unroll
-        for (int it = 0; it < PERX; ++it) {
-            const int i = tid + it * DC_THREADS, t = i / DV, j = i % DV;
-            G1[t * FY + j] = be[t] * (vv[it] - ela[t] * G1[t * FY + j]);
-            G2[t * FY + j] *= ela[t];
         }
         __syncthreads();
         // (I + A) U = right-hand side, 16 rows at a time
@@ -251,44 +286,40 @@ delta_rule_chunked_kernel(const float* __restrict__ qg, const float* __restrict_
             if (bi > 0) {
                 if (warp < DT) {                       // what the blocks before contribute leaves the right-hand side
                     FragC acc;
-                    wmma::load_matrix_sync(acc, G1 + bi * 16 * FY + warp * 16, FY, wmma::mem_row_major);
+                    wmma::load_matrix_sync(acc, R1 + bi * 16 * FD + warp * 16, FD, wmma::mem_row_major);
                     dc_mma3<FragA, FragB>(acc, NH + bi * 16 * LQ, NL + bi * 16 * LQ, LQ, 16, UH + warp * 16, UL + warp * 16,
                                           LD, 16 * LD, bi);
-                    wmma::store_matrix_sync(G1 + bi * 16 * FY + warp * 16, acc, FY, wmma::mem_row_major);
+                    wmma::store_matrix_sync(R1 + bi * 16 * FD + warp * 16, acc, FD, wmma::mem_row_major);
                 }
                 __syncthreads();
             }
-            constexpr int PERU = 16 * DV / DC_THREADS;
-            float u[PERU];
 #pragma unroll
-            for (int it = 0; it < PERU; ++it) {
-                const int o = tid + it * DC_THREADS, t = o / DV, j = o % DV;
-                const float* mrow = Md + bi * 256 + t * 16;
-                float acc = 0.f;
+            for (int o = tid; o < 16 * DV; o += DC_THREADS) {
+                const int tl = o / DV, j = o % DV, t = bi * 16 + tl;
+                const float* mrow = Md + bi * 256 + tl * 16;
+                float u0 = 0.f, u1 = 0.f;
 #pragma unroll
-                for (int s = 0; s < 16; ++s) acc = fmaf(mrow[s], G1[(bi * 16 + s) * FY + j], acc);   // zeros above the diagonal
-                u[it] = acc;
-            }
-            __syncthreads();
-#pragma unroll
-            for (int it = 0; it < PERU; ++it) {
-                const int o = tid + it * DC_THREADS, t = bi * 16 + o / DV, j = o % DV;
-                G1[t * FY + j] = u[it];
-                dc_split(u[it], UH + t * LD + j, UL + t * LD + j);
-                dc_split(u[it] * wv[t], WH + t * LD + j, WL + t * LD + j);
+                for (int s = 0; s < 16; s += 2) {      // zeros above the diagonal
+                    u0 = fmaf(mrow[s], R1[(bi * 16 + s) * FD + j], u0);
+                    u1 = fmaf(mrow[s + 1], R1[(bi * 16 + s + 1) * FD + j], u1);
+                }
+                const float u = u0 + u1;
+                dc_split(u, UH + t * LD + j, UL + t * LD + j);
+                dc_split(u * wv[t], WH + t * LD + j, WL + t * LD + j);
             }
             __syncthreads();
         }
-        // O = exp(l_t) Q S_0 + P U
-        for (int job = warp; job < 4 * DT; job += DC_WARPS) {
-            const int ti = job / DT, tj = job % DT;
+        // O = exp(l_t) Q S_0 + P U, the tiles with the most steps first and dealt from the last warp down (the state's
+        // tiles below are dealt from the first warp up)
+        for (int job = DC_WARPS - 1 - warp; job < 4 * DT; job += DC_WARPS) {
+            const int ti = 3 - job / DT, tj = job % DT;
             FragC acc;
-            wmma::load_matrix_sync(acc, G2 + ti * 16 * FY + tj * 16, FY, wmma::mem_row_major);
+            wmma::load_matrix_sync(acc, R2 + ti * 16 * FD + tj * 16, FD, wmma::mem_row_major);
             dc_mma3<FragA, FragB>(acc, PH + ti * 16 * LQ, PL + ti * 16 * LQ, LQ, 16, UH + tj * 16, UL + tj * 16, LD, 16 * LD,
                                   ti + 1);
-            wmma::store_matrix_sync(G2 + ti * 16 * FY + tj * 16, acc, FY, wmma::mem_row_major);
+            wmma::store_matrix_sync(R2 + ti * 16 * FD + tj * 16, acc, FD, wmma::mem_row_major);
         }
-        // S = exp(l_Q) S + K^T (w * U); a tile of the state belongs to one warp
+        // S = exp(l_Q) S + K^T (w * U); a tile of the state belongs to one warp, which also makes its two halves
         const float dec_end = ela[DC_Q - 1];
         for (int job = warp; job < (NP / 16) * DT; job += DC_WARPS) {
             const int ni = job / DT, tj = job % DT;
@@ -298,15 +329,16 @@ delta_rule_chunked_kernel(const float* __restrict__ qg, const float* __restrict_
             dc_mma3<FragAT, FragB>(acc, KH + ni * 16, KL + ni * 16, LN, 16 * LN, WH + tj * 16, WL + tj * 16, LD, 16 * LD,
                                    DC_Q / 16);
             wmma::store_matrix_sync(Sf + ni * 16 * FD + tj * 16, acc, FD, wmma::mem_row_major);
+            __syncwarp();
+            for (int x = lane; x < 256; x += 32) {
+                const int n = ni * 16 + (x >> 4), j = tj * 16 + (x & 15);
+                dc_split(Sf[n * FD + j], SH + n * LD + j, SL + n * LD + j);
+            }
         }
         __syncthreads();
         for (int i = tid; i < DC_Q * DV; i += DC_THREADS) {
             const int t = i / DV, j = i % DV;
-            if (t < nt && col0 + j < e) out[((size_t)(a0 + t0 + t) * H + h) * e + col0 + j] = G2[t * FY + j];
-        }
-        for (int i = tid; i < NP * DV; i += DC_THREADS) {
-            const int n = i / DV, j = i % DV;
-            dc_split(Sf[n * FD + j], SH + n * LD + j, SL + n * LD + j);
+            if (t < nt && col0 + j < e) out[((size_t)(a0 + t0 + t) * H + h) * e + col0 + j] = R2[t * FD + j];
         }
     }
     __syncthreads();
@@ -321,7 +353,7 @@ delta_rule_chunked_kernel(const float* __restrict__ qg, const float* __restrict_
 template <int NP, int DV> static size_t dc_smem() {
     const int LN = NP + DC_PAD, LD = DV + DC_PAD, LQ = DC_Q + DC_PAD, FY = DC_Q + DC_PADF, FD = DV + DC_PADF;
     return (size_t)(4 * DC_Q * LN + 2 * NP * LD + 4 * DC_Q * LQ + 4 * DC_Q * LD) * sizeof(bf16) +
-           (size_t)(2 * DC_Q * FY + NP * FD + 8 * 256 + 4 * DC_Q) * sizeof(float);
+           (size_t)(2 * DC_Q * FY + 2 * DC_Q * FD + NP * FD + 8 * 256 + 4 * DC_Q) * sizeof(float);
 }
 
 // q, k [T, .] with head h's d channels at column (h / (H / G)) d of rows `ld` floats apart; v likewise with e columns a
@@ -335,11 +367,15 @@ extern "C" int aie_delta_rule_chunked(const float* q, const float* k, const floa
     if (R <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G || d <= 0 || e <= 0) return AIE_BAD_ARG;
     if (d > 128) return AIE_UNSUPPORTED;
-    // 64 value columns a CTA where the state's rows leave room for them and every SM still gets a CTA, else 32
-    const bool narrow = d > 64 || (e > 32 && (long long)R * H * ((e + 63) / 64) < aie_sm_count());
-    const int DVc = narrow ? 32 : 64, col_blocks = (e + DVc - 1) / DVc;
+    // value columns a CTA: the widest of 64, 32 and 16 that the state's rows leave room for and that gives every SM a
+    // CTA; narrower CTAs repeat the products of keys and queries, but a lone long prompt has few (request, head) pairs
+    const int sms = aie_sm_count();
+    int DVc = d > 64 ? 32 : 64;
+    while (DVc > 16 && e > DVc / 2 && (long long)R * H * ((e + DVc - 1) / DVc) < sms) DVc /= 2;
+    const int col_blocks = (e + DVc - 1) / DVc;
     const long long blocks = (long long)R * H * col_blocks;
     if (blocks > 0x7fffffffLL) return AIE_UNSUPPORTED;
+    const int vec4 = d % 4 == 0 && ld % 4 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)k & 15) == 0;
 #define GO(NP, DV)                                                                                                      \
     do {                                                                                                                \
         static bool set = false;                                                                                        \
@@ -351,17 +387,18 @@ extern "C" int aie_delta_rule_chunked(const float* q, const float* k, const floa
         }                                                                                                               \
         delta_rule_chunked_kernel<NP, DV><<<(unsigned)blocks, DC_THREADS, dc_smem<NP, DV>(), st>>>(                     \
             q, k, v, ld, b_raw, ldb, a_raw, lda, a_log, dt_bias, q_scale, unit_eps, state, out, q_start, q_len, slots,  \
-            live, H, G, d, e, col_blocks, max_slots, min_len, err);                                                     \
+            live, H, G, d, e, col_blocks, max_slots, min_len, vec4, err);                                                \
     } while (0)
-    if (d <= 32) {
-        if (narrow) GO(32, 32);
-        else GO(32, 64);
-    } else if (d <= 64) {
-        if (narrow) GO(64, 32);
-        else GO(64, 64);
-    } else {
-        GO(128, 32);
-    }
+#define GO3(NP)                                  \
+    do {                                         \
+        if (DVc == 64) GO(NP < 128 ? NP : 64, 64); \
+        else if (DVc == 32) GO(NP, 32);          \
+        else GO(NP, 16);                         \
+    } while (0)
+    if (d <= 32) GO3(32);
+    else if (d <= 64) GO3(64);
+    else GO3(128);
+#undef GO3
 #undef GO
     AIE_LAUNCH_CHECK();
 }

@@ -223,8 +223,10 @@ def test_delta_rule_state_against_the_oracle():
         assert float((S[a] - keep[a]).abs().max()) < 1e-5
 
 
+# heads and sizes that between them reach every pair of (padded rows of the state, value columns a CTA) the launcher picks
 @pytest.mark.parametrize("sizes", [(4, 2, 24, 20), (2, 1, 64, 64), (2, 2, 128, 72), (3, 1, 40, 100), (1, 1, 32, 32),
-                                   (148, 4, 16, 40)])
+                                   (148, 4, 16, 40), (40, 4, 64, 64), (20, 5, 128, 64), (20, 2, 48, 64), (20, 20, 20, 64),
+                                   (2, 1, 126, 30)])
 def test_delta_rule_in_chunks_against_token_by_token(sizes):
     """The chunked kernel and the token-by-token kernel on the same float32 inputs, from the same non-zero state,
     agree to float32 rounding times the chunk's length: a portion of several chunks with a ragged end, a portion of
