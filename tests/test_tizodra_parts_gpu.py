@@ -262,3 +262,44 @@ def test_delta_rule_in_chunks_against_token_by_token(sizes):
         diff = (a - b).abs()
         assert float(diff.max()) <= 3e-4 * spread, f"{what} {sizes}: {float(diff.max()):.3e} of spread {spread:.3e} at {int(diff.flatten().argmax())}"
     assert float((s1 - S0.double().cpu()).abs().max()) > 1e-3       # the states did move
+
+
+@pytest.mark.parametrize("chunked", [False, True])
+def test_delta_rule_recalls_a_pair_written_hundreds_of_tokens_back(chunked):
+    """Closed form: with decays of one and full write strength, a value written along a key that no later key
+    touches is read back whole by a query along that key, 285 tokens and several chunks later and across two steps;
+    a query orthogonal to every key reads nothing.  A state that is lost between chunks or steps, or decayed once
+    too often, shows at once."""
+    from ai_engine_b200.kernels import ops
+    H, G, d, e, T, at, ask = 2, 1, 64, 48, 300, 5, 290
+    gen = torch.Generator().manual_seed(7)
+    part, _ = delta_part(dict(heads=H, kv_heads=G, dim=d, vdim=e, conv=2), 16, 1e-5, "bfloat16", gen)
+    rig = Rig(part, torch.bfloat16, page=8, pages=64, max_seqs=2)
+    star = torch.zeros(d)
+    star[3] = 1.0
+    spare = torch.zeros(d)
+    spare[4] = 1.0
+    k = torch.randn(T, d, generator=gen)
+    k[:, 3] = 0.0                                        # no other key has a share along the planted one
+    k[:, 4] = 0.0                                        # ... nor along the spare direction
+    k[at] = star * 3.0                                   # any length: the kernel makes it a unit vector
+    q = torch.randn(T, d, generator=gen)
+    q[ask] = star * 0.5
+    q[ask + 1] = spare
+    v = torch.randn(T, H * e, generator=gen)
+    qkv = torch.cat([q, k, v], dim=1).to(DEV)
+    b_raw = torch.full((T, H), 30.0, device=DEV)         # beta = 1
+    a_raw = torch.full((T, H), -60.0, device=DEV)        # softplus = 0: no decay
+    a_log, dt_bias = torch.zeros(H, device=DEV), torch.zeros(H, device=DEV)
+    slot = rig.admit()
+    outs = []
+    for n0, n in ((0, 100), (100, 200)):
+        ctx, lc = rig.step([(slot, n)])
+        rows = qkv[n0:n0 + n]
+        outs.append(ops.delta_rule(rows[:, :d], rows[:, d:2 * d], rows[:, 2 * d:], b_raw[n0:n0 + n], a_raw[n0:n0 + n],
+                                   a_log, dt_bias, d ** -0.5, 1e-6, lc.state["S"], ctx, H, G, d, e, chunked=chunked))
+        rig.done([(slot, n)])
+    o = torch.cat(outs).cpu().double().reshape(T, H * e)
+    want = v[at].double() * d ** -0.5
+    assert float((o[ask] - want).abs().max()) < 2e-4 * float(want.abs().max())
+    assert float(o[ask + 1].abs().max()) < 2e-4 * float(want.abs().max())
