@@ -220,3 +220,60 @@ def test_the_trace_program_and_the_command_line_on_a_tizodra_folder(tmp_path):
                 "head_norm_gate", "activate", "scale"):
         assert cls in p.stderr, cls
     greedy_matches(CONFIGS["A"], read_tensors(d), [5, 17, 3, 200], lines[0], 5)
+
+
+def drawn_config(seed):
+    """A configuration drawn at random: 2-6 layers of either kind in any order, any sizes (also ones the tensor-core
+    kernels do not take), windows shorter than a page or none, kept tokens beyond the window, a loop anywhere or none."""
+    import random
+    from tizodra_helpers import attn, delta, layer
+    r = random.Random(seed)
+    width = r.choice([32, 44, 64, 72, 100, 128, 160])
+    layers = []
+    for _ in range(r.randint(2, 6)):
+        heads = r.choice([1, 2, 3, 4, 6, 8])
+        kv = r.choice([k for k in (1, 2, 3, 4, 6, 8) if heads % k == 0])
+        ff = r.choice([None, 24, 40, 96, 200])
+        if r.random() < 0.5:
+            dim, vdim = r.choice([8, 12, 32, 40, 64, 96, 128]), r.choice([4, 16, 32, 36, 64, 128])
+            size = r.choice([None, 1, 3, 17, 40, 64, 100])
+            layers.append(layer(attn(heads, kv, dim, vdim, r.uniform(0.05, 0.4), size,
+                                     r.choice([0, 1, 4, 20, 70]) if size else None), ff))
+        else:
+            layers.append(layer(delta(heads, kv, r.choice([8, 20, 32, 48, 64, 128, 136]),
+                                      r.choice([8, 16, 24, 64, 80, 128]), r.randint(1, 5)), ff))
+    cfg = dict(architecture="Tizodra", vocab=r.choice([61, 128, 300]), width=width,
+               norm=dict(eps=r.choice([1e-6, 1e-5, 1e-3])), logit_scale=r.choice([0.25, 1.0, 2.5]), layers=layers)
+    if r.random() < 0.8:
+        start = r.randint(0, len(layers) - 1)
+        cfg["loop"] = dict(start=start, stop=r.randint(start + 1, len(layers)), times=r.randint(1, 3))
+    return cfg
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_configurations_drawn_at_random(tmp_path, seed):
+    """float32 against the float64 oracle at every row; bfloat16 against the float32 oracle: whole, in portions beside
+    a second request that decodes, and the two schedules of the bfloat16 engine against each other."""
+    name = f"R{seed}"
+    CONFIGS[name] = drawn_config(seed)
+    d = make_dir(tmp_path, name, seed=seed)
+    vocab = CONFIGS[name]["vocab"]
+    ids, other = ids_for(170, vocab, 100 + seed), ids_for(60, vocab, 200 + seed)
+    for dtype in ("float32", "bfloat16"):
+        ref, ref_o = (plain_logits(d, name, x, oracle_dtype(dtype)) for x in (ids, other))
+        rep = replayer(d, dtype, 320)
+        close(feed(rep, "w", ids, [170]), ref, dtype, f"drawn {seed} {dtype} whole")
+        cuts, got, got_o, at, at_o = [40, 2, 33, 1, 1, 64, 29], [], [], 0, 0
+        for k, n in enumerate(cuts):                 # portions of one request beside a prompt, then single tokens, of another
+            m = 20 if k == 0 else (1 if at_o < 60 else 0)
+            entries = [dict(id="p", tokens=ids[at:at + n], want=list(range(n)))]
+            if m:
+                entries.append(dict(id="o", tokens=other[at_o:at_o + m], want=list(range(m))))
+            out = rep.run_step(entries, []).numpy().astype(np.float64)
+            got.append(out[:n])
+            got_o.append(out[n:n + m])
+            at, at_o = at + n, at_o + m
+        rep.run_step([], ["p", "o"])
+        close(np.concatenate(got), ref, dtype, f"drawn {seed} {dtype} in portions")
+        close(np.concatenate(got_o), ref_o[:at_o], dtype, f"drawn {seed} {dtype} the request beside")
+        rep.cache.book.check_invariants()
