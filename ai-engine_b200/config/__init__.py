@@ -15,3 +15,6 @@ __all__.append("ZupitarConfig")
 from .tizodra import TizodraConfig  # noqa: E402
 
 __all__.append("TizodraConfig")
+from .fokisun import FokisunConfig  # noqa: E402
+
+__all__.append("FokisunConfig")

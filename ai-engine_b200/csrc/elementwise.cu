@@ -547,3 +547,92 @@ extern "C" int aie_join_streams(const float* x, const void* delta, int delta_dty
 #undef AIE_JS
     AIE_LAUNCH_CHECK();
 }
+
+// ---------------------------------------------------------------------------
+// Dynamic Tanh, a norm without statistics: s = x[row] (+ delta, or the sum of `parts` deltas);
+//   out = tanh(alpha * s) * w + b          element by element, float32, rounded once.
+// alpha is read from the device (one float).  `rows` (optional) picks input rows; `write_back` stores s into x.
+// ---------------------------------------------------------------------------
+template <typename A, typename O>
+__global__ void add_dyt_kernel(float* __restrict__ x, const A* __restrict__ delta, int parts, size_t part_stride,
+                               const float* __restrict__ w, const float* __restrict__ b, const float* __restrict__ alpha,
+                               O* __restrict__ out, const int* __restrict__ rows, int D, int write_back, size_t n) {
+    const float al = alpha[0];
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) {
+        const size_t o = i / D;
+        const int c = (int)(i - o * D);
+        const size_t at = (rows ? (size_t)rows[o] : o) * D + c;
+        float s = x[at];
+        if (delta) {
+            for (int p = 0; p < parts; ++p) s += to_f32<A>(delta[p * part_stride + at]);
+            if (write_back) x[at] = s;
+        }
+        out[i] = from_f32<O>(fmaf(tanhf(al * s), w[c], b[c]));
+    }
+}
+
+extern "C" int aie_add_dyt(float* x, const void* delta, int delta_dtype, int parts, long long part_stride, const float* w,
+                           const float* b, const float* alpha, void* out, int out_dtype, const int* rows, int n_rows, int D,
+                           int write_back, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (D <= 0 || (delta && parts < 1)) return AIE_BAD_ARG;
+    const size_t n = (size_t)n_rows * D;
+    int blocks = (int)((n + 255) / 256);
+    if (blocks > aie_sm_count() * 16) blocks = aie_sm_count() * 16;
+#define GO(A, O)                                                                                                      \
+    add_dyt_kernel<A, O><<<blocks, 256, 0, stream>>>(x, (const A*)delta, parts, (size_t)part_stride, w, b, alpha,     \
+                                                     (O*)out, rows, D, write_back, n)
+    const bool dbf = delta && delta_dtype == AIE_BF16;
+    if (out_dtype == AIE_F32) { if (dbf) GO(bf16, float); else GO(float, float); }
+    else if (out_dtype == AIE_BF16) { if (dbf) GO(bf16, bf16); else GO(float, bf16); }
+    else return AIE_BAD_ARG;
+#undef GO
+    AIE_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------
+// a[t, n] <- a[t, n] * sigmoid(g[t, n / group])   in place; g float32 with rows `ldg` floats apart (a slice of a
+// wider projection).  group 1: a gate per element; group = a head's width: a gate per head.
+// ---------------------------------------------------------------------------
+template <typename A>
+__global__ void sigmoid_gate_mul_kernel(A* __restrict__ a, const float* __restrict__ g, int ldg, int N, int group, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) {
+        const size_t t = i / N;
+        const int c = (int)(i - t * N);
+        const float z = g[t * ldg + c / group];
+        a[i] = from_f32<A>(to_f32<A>(a[i]) * (1.0f / (1.0f + expf(-z))));
+    }
+}
+
+extern "C" int aie_sigmoid_gate_mul(void* a, int dtype, const float* g, int ldg, int T, int N, int group, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (N <= 0 || group <= 0 || N % group) return AIE_BAD_ARG;
+    const size_t n = (size_t)T * N;
+    int blocks = (int)((n + 255) / 256);
+    if (blocks > aie_sm_count() * 16) blocks = aie_sm_count() * 16;
+    if (dtype == AIE_F32) sigmoid_gate_mul_kernel<float><<<blocks, 256, 0, stream>>>((float*)a, g, ldg, N, group, n);
+    else if (dtype == AIE_BF16) sigmoid_gate_mul_kernel<bf16><<<blocks, 256, 0, stream>>>((bf16*)a, g, ldg, N, group, n);
+    else return AIE_BAD_ARG;
+    AIE_LAUNCH_CHECK();
+}
+
+// y[t, n] += bias[n] in place, float32 (a projection's bias, added to the first of its unjoined parts)
+__global__ void add_bias_kernel(float* __restrict__ y, const float* __restrict__ bias, int N, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) y[i] += bias[i % N];
+}
+
+extern "C" int aie_add_bias(float* y, const float* bias, int T, int N, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (N <= 0) return AIE_BAD_ARG;
+    const size_t n = (size_t)T * N;
+    int blocks = (int)((n + 255) / 256);
+    if (blocks > aie_sm_count() * 16) blocks = aie_sm_count() * 16;
+    add_bias_kernel<<<blocks, 256, 0, stream>>>(y, bias, N, n);
+    AIE_LAUNCH_CHECK();
+}

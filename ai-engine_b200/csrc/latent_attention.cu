@@ -8,12 +8,28 @@
 // latent_prepare: from the fused projection [q heads | c | kr] of the step's tokens it writes the plain
 //   query parts (compute dtype, for the folding product), the rotated query parts (float32), and the
 //   normalised c and rotated kr into the token's cache row.  The rotation pairs element 2i with 2i+1 over the
-//   first `rot_dims` elements of the rot-wide part; the angle is float(position) * inv_freq[i] in float32.
+//   first `rot_dims` elements of the rot-wide part (or, with `halves`, element i with i + rot_dims / 2); the
+//   angle is float(position) * inv_freq[i] in float32.  The latent and the key part may come from a projection
+//   of their own (`kv`, rows ld_kv floats apart) when the queries are made by a second product.
 // latent_attention: one block per (token, head); keys in chunks of 128 that start at multiples of 128 of the
 //   absolute key position with a running maximum and sum, so a row's additions depend on its position only.
 #include "common.cuh"
 
 #define LAT_CHUNK 128
+
+// element i of a rot-wide vector x after the rotation by `pos`
+__device__ __forceinline__ float latent_rotated(const float* x, int i, int half, int halves, int pos,
+                                                const float* __restrict__ inv_freq) {
+    if (i >= 2 * half) return x[i];
+    float sn, cs;
+    if (halves) {
+        const int j = i < half ? i : i - half;
+        sincosf((float)pos * inv_freq[j], &sn, &cs);
+        return i < half ? x[i] * cs - x[i + half] * sn : x[i] * cs + x[j] * sn;
+    }
+    sincosf((float)pos * inv_freq[i >> 1], &sn, &cs);
+    return (i & 1) ? x[i] * cs + x[i - 1] * sn : x[i] * cs - x[i + 1] * sn;
+}
 
 template <typename A, typename C>
 __global__ void latent_prepare_kernel(const float* __restrict__ proj, int ld, int H, int d, int rot, int rank,
@@ -22,7 +38,7 @@ __global__ void latent_prepare_kernel(const float* __restrict__ proj, int ld, in
                                       float* __restrict__ q_full, C* __restrict__ pages,
                                       const int* __restrict__ positions, const int* __restrict__ token_req,
                                       const int* __restrict__ block_table, int bt_width, int num_pages, int P,
-                                      unsigned* err) {
+                                      unsigned* err, const float* __restrict__ kv, int ld_kv, int halves) {
     __shared__ float red[32];
     const int t = blockIdx.x, tid = threadIdx.x;
     const float* row = proj + (size_t)t * ld;
@@ -36,16 +52,10 @@ __global__ void latent_prepare_kernel(const float* __restrict__ proj, int ld, in
     for (int e = tid; e < H * rot; e += blockDim.x) {
         const int hh = e / rot, i = e % rot;
         const float* qr = row + hh * dq + d;
-        float v = qr[i];
-        if (i < 2 * half) {
-            float sn, cs;
-            sincosf((float)pos * inv_freq[i >> 1], &sn, &cs);
-            v = (i & 1) ? qr[i] * cs + qr[i - 1] * sn : qr[i] * cs - qr[i + 1] * sn;
-        }
-        q_full[((size_t)t * H + hh) * dk + rank + i] = v;
+        q_full[((size_t)t * H + hh) * dk + rank + i] = latent_rotated(qr, i, half, halves, pos, inv_freq);
     }
     if (!has_kv) return;
-    const float* z = row + H * dq;
+    const float* z = kv ? kv + (size_t)t * ld_kv : row + H * dq;
     float ss = 0.f;
     for (int i = tid; i < rank; i += blockDim.x) ss += z[i] * z[i];
     ss = block_sum(ss, red);
@@ -59,28 +69,20 @@ __global__ void latent_prepare_kernel(const float* __restrict__ proj, int ld, in
     C* dst = pages + ((size_t)page * P + (pos - pidx * P)) * dk;
     for (int i = tid; i < rank; i += blockDim.x) dst[i] = from_f32<C>((z[i] * rinv) * c_weight[i]);
     const float* kr = z + rank;
-    for (int i = tid; i < rot; i += blockDim.x) {
-        float v = kr[i];
-        if (i < 2 * half) {
-            float sn, cs;
-            sincosf((float)pos * inv_freq[i >> 1], &sn, &cs);
-            v = (i & 1) ? kr[i] * cs + kr[i - 1] * sn : kr[i] * cs - kr[i + 1] * sn;
-        }
-        dst[rank + i] = from_f32<C>(v);
-    }
+    for (int i = tid; i < rot; i += blockDim.x) dst[rank + i] = from_f32<C>(latent_rotated(kr, i, half, halves, pos, inv_freq));
 }
 
 extern "C" int aie_latent_prepare(const float* proj, int ld, int T, int H, int d, int rot, int rank, int rot_dims,
                                   int has_kv, const float* c_weight, float eps, const float* inv_freq, void* q_plain,
                                   int q_dtype, float* q_full, void* pages, int cache_dtype, const int* positions,
                                   const int* token_req, const int* block_table, int bt_width, int num_pages, int P,
-                                  unsigned* err, cudaStream_t st) {
+                                  unsigned* err, const float* kv, int ld_kv, int halves, cudaStream_t st) {
     if (T <= 0) return 0;
     if (rot_dims % 2 || rot_dims > rot || H <= 0 || d < 0 || rank <= 0) return AIE_BAD_ARG;
 #define GO(A, C)                                                                                                      \
     latent_prepare_kernel<A, C><<<T, 128, 0, st>>>(proj, ld, H, d, rot, rank, rot_dims, has_kv, c_weight, eps, inv_freq, \
                                                    (A*)q_plain, q_full, (C*)pages, positions, token_req, block_table,  \
-                                                   bt_width, num_pages, P, err)
+                                                   bt_width, num_pages, P, err, kv, ld_kv, halves)
     if (q_dtype == AIE_F32 && cache_dtype == AIE_F32) GO(float, float);
     else if (q_dtype == AIE_BF16 && cache_dtype == AIE_BF16) GO(bf16, bf16);
     else if (q_dtype == AIE_BF16 && cache_dtype == AIE_F32) GO(bf16, float);

@@ -5,7 +5,10 @@
 // per token and head made here from a step size (a selective state space: dt = softplus(raw + bias),
 // a = exp(-exp(a_log) dt), the value scaled by dt, queries and keys shared by `hpg` neighbouring heads, and
 // skip[h] v added to the output).  The state is float32, lives in the request's slot and is carried from step
-// to step.
+// to step.  A fourth form has no keys: what the forget gate lets go is what is written (fg_lower given):
+// a_t = l + (1 - l) sigmoid(z_t + bias) with a lower bound l per channel, k_t = 1 - a_t, and the query is
+// silu of its projection; z comes in place of the per-token decays, and the three are made in float32 while a
+// token's rows are staged.
 //
 // The columns of S never mix: column j needs only v_t[j].  A warp owns 32 / lanes columns of one (request,
 // head); `lanes` threads share a column, each with RPT consecutive rows of S in registers, and a token costs
@@ -43,7 +46,8 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
                          const int* __restrict__ q_start, const int* __restrict__ q_len, const int* __restrict__ slots,
                          int H, int d, int dv, int lanes, int groups, int TT, int max_slots, int vec, int vec4, unsigned* err,
                          int hpg, const float* __restrict__ dt_raw, int ld_dt, const float* __restrict__ dt_bias,
-                         const float* __restrict__ a_log, const float* __restrict__ skip, int max_len) {
+                         const float* __restrict__ a_log, const float* __restrict__ skip, int max_len,
+                         const float* __restrict__ fg_lower, const float* __restrict__ fg_bias) {
     extern __shared__ __align__(16) float lr_sm[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int bg = blockIdx.x % groups, h = (blockIdx.x / groups) % H, r = blockIdx.x / (groups * H);
@@ -99,14 +103,26 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
             if (vec4) {
                 for (int c = lane * 4; c < d; c += 128) {
                     *reinterpret_cast<float4*>(q_s + tok * d + c) = *reinterpret_cast<const float4*>(q + at + c);
-                    *reinterpret_cast<float4*>(k_s + tok * d + c) = *reinterpret_cast<const float4*>(k + at + c);
+                    if (k) *reinterpret_cast<float4*>(k_s + tok * d + c) = *reinterpret_cast<const float4*>(k + at + c);
                     if (decay_tok) *reinterpret_cast<float4*>(a_s + tok * d + c) = *reinterpret_cast<const float4*>(decay_tok + at_a + c);
                 }
             } else {
                 for (int c = lane; c < d; c += 32) {
                     q_s[tok * d + c] = q[at + c];
-                    k_s[tok * d + c] = k[at + c];
+                    if (k) k_s[tok * d + c] = k[at + c];
                     if (decay_tok) a_s[tok * d + c] = decay_tok[at_a + c];
+                }
+            }
+            if (fg_lower) {                                        // gate, key and query of the keyless form
+                __syncwarp();
+                for (int c = lane; c < d; c += 32) {
+                    const float lo = fg_lower[h * d + c];
+                    const float z = a_s[tok * d + c] + (fg_bias ? fg_bias[h * d + c] : 0.f);
+                    const float f = lo + (1.0f - lo) * (1.0f / (1.0f + expf(-z)));
+                    a_s[tok * d + c] = f;
+                    k_s[tok * d + c] = 1.0f - f;
+                    const float qq = q_s[tok * d + c];
+                    q_s[tok * d + c] = qq / (1.0f + expf(-qq));
                 }
             }
             for (int c = lane; c < CB; c += 32)
@@ -266,9 +282,10 @@ extern "C" int aie_linear_recurrence(const float* q, const float* k, const float
                                      float* out, const int* q_start, const int* q_len, const int* slots, int T, int R,
                                      int H, int d, int dv, int max_slots, unsigned* err, int hpg, const float* dt_raw,
                                      int ld_dt, const float* dt_bias, const float* a_log, const float* skip, int max_len,
-                                     int wide_state, cudaStream_t st) {
+                                     int wide_state, const float* fg_lower, const float* fg_bias, cudaStream_t st) {
     if (R <= 0) return 0;
     if (H <= 0 || d <= 0 || dv <= 0 || (!decay_tok && !decay_head && !dt_raw)) return AIE_BAD_ARG;
+    if (fg_lower ? (!decay_tok || k || hpg != 1) : !k) return AIE_BAD_ARG;
     if (hpg < 1 || H % hpg || (dt_raw && (!dt_bias || !a_log || decay_tok))) return AIE_BAD_ARG;
     if (d > 1024) return AIE_UNSUPPORTED;
     // a step of single tokens in the state-space form: the kernel that reads rows of the state whole
@@ -308,13 +325,13 @@ extern "C" int aie_linear_recurrence(const float* q, const float* k, const float
                                                                      q_scale, k_scale, state, out, q_start, q_len,  \
                                                                      slots, H, d, dv, lanes, groups, TT, max_slots, \
                                                                      vec, vec4, err, hpg, dt_raw, ld_dt, dt_bias,   \
-                                                                     a_log, skip, max_len);                         \
+                                                                     a_log, skip, max_len, fg_lower, fg_bias);      \
     else                                                                                                            \
         linear_recurrence_kernel<N, float><<<(unsigned)blocks, LR_THREADS, smem, st>>>(q, k, v, ld, decay_tok, ld_decay, decay_head,  \
                                                                      q_scale, k_scale, state, out, q_start, q_len,  \
                                                                      slots, H, d, dv, lanes, groups, TT, max_slots, \
                                                                      vec, vec4, err, hpg, dt_raw, ld_dt, dt_bias,   \
-                                                                     a_log, skip, max_len);                         \
+                                                                     a_log, skip, max_len, fg_lower, fg_bias);      \
     } while (0)
     if (rpt == 4) GO(4);
     else if (rpt == 8) GO(8);

@@ -147,6 +147,37 @@ __global__ void depth_average_kernel(float* __restrict__ x, const A* __restrict_
     x[i] = fmaf(coef[depth], s, acc);
 }
 
+// Two branches that read the same input, added to the stream with one multiplier:
+//   X = x + mult * (sum of a's parts + sum of b's parts), then as above.  a and b are float32; b may be absent.
+// With norm_w: also out = tanh(alpha x) w + b_n of the averaged stream (the next layer's input norm, when that is a
+// norm without statistics), so the stream is not read again.
+template <typename O>
+__global__ void depth_average2_kernel(float* __restrict__ x, const float* __restrict__ a, int pa, size_t sa,
+                                      const float* __restrict__ b, int pb, size_t sb, float mult,
+                                      float* __restrict__ history, const float* __restrict__ coef, int depth, size_t n,
+                                      const float* __restrict__ norm_w, const float* __restrict__ norm_b,
+                                      const float* __restrict__ norm_alpha, O* __restrict__ normed, int D) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float d = 0.f;
+    for (int p = 0; p < pa; ++p) d += a[p * sa + i];
+    float e = 0.f;
+    for (int p = 0; p < pb; ++p) e += b[p * sb + i];
+    const float s = fmaf(mult, d + e, x[i]);
+    float y = s;
+    if (coef) {
+        history[(size_t)depth * n + i] = s;
+        float acc = 0.f;
+        for (int j = 0; j < depth; ++j) acc = fmaf(coef[j], history[(size_t)j * n + i], acc);
+        y = fmaf(coef[depth], s, acc);
+    }
+    x[i] = y;
+    if (norm_w) {
+        const int c = (int)(i % D);
+        normed[i] = from_f32<O>(fmaf(tanhf(norm_alpha[0] * y), norm_w[c], norm_b[c]));
+    }
+}
+
 extern "C" int aie_depth_average(float* x, const void* delta, int delta_dtype, int parts, long long part_stride,
                                  float* history, const float* coef, int depth, long long n, cudaStream_t st) {
     if (n <= 0) return 0;
@@ -157,6 +188,25 @@ extern "C" int aie_depth_average(float* x, const void* delta, int delta_dtype, i
         depth_average_kernel<bf16><<<blocks, 256, 0, st>>>(x, (const bf16*)delta, parts, (size_t)part_stride, history, coef, depth, (size_t)n);
     else
         depth_average_kernel<float><<<blocks, 256, 0, st>>>(x, (const float*)delta, parts, (size_t)part_stride, history, coef, depth, (size_t)n);
+    AIE_LAUNCH_CHECK();
+}
+
+// coef null: no averaging (x <- X).  norm_w null: no norm is made.
+extern "C" int aie_depth_average2(float* x, const float* a, int pa, long long sa, const float* b, int pb, long long sb,
+                                  float mult, float* history, const float* coef, int depth, long long n,
+                                  const float* norm_w, const float* norm_b, const float* norm_alpha, void* normed,
+                                  int normed_dtype, int D, cudaStream_t st) {
+    if (n <= 0) return 0;
+    if (depth < 0 || !a || pa < 1 || (coef && !history) || (norm_w && (!norm_b || !norm_alpha || !normed || D <= 0)))
+        return AIE_BAD_ARG;
+    if (!b) pb = 0;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (norm_w && normed_dtype == AIE_BF16)
+        depth_average2_kernel<bf16><<<blocks, 256, 0, st>>>(x, a, pa, (size_t)sa, b, pb, (size_t)sb, mult, history, coef, depth,
+                                                           (size_t)n, norm_w, norm_b, norm_alpha, (bf16*)normed, D);
+    else
+        depth_average2_kernel<float><<<blocks, 256, 0, st>>>(x, a, pa, (size_t)sa, b, pb, (size_t)sb, mult, history, coef, depth,
+                                                            (size_t)n, norm_w, norm_b, norm_alpha, (float*)normed, D ? D : 1);
     AIE_LAUNCH_CHECK();
 }
 
@@ -203,8 +253,8 @@ extern "C" int aie_polynorm(const float* z, const float* coef, void* out, int ou
 }
 
 // ---------------------------------------------------------------------------
-// Per (token, head): y = o / sqrt(mean(o^2) + eps) (* w) * silu(g).  o [T, H, dv] float32; g has rows of
-// `ldg` floats (a slice of a wider projection); w [dv] or null.  One warp per (token, head).
+// Per (token, head): y = o / sqrt(mean(o^2) + eps) (* w) (* silu(g)).  o [T, H, dv] float32; g has rows of
+// `ldg` floats (a slice of a wider projection) or is null (no gate); w [dv] or null.  One warp per (token, head).
 // ---------------------------------------------------------------------------
 template <typename O>
 __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ g, int ldg,
@@ -217,12 +267,15 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* 
     for (int i = lane; i < dv; i += 32) ss += orow[i] * orow[i];
     ss = warp_sum(ss);
     const float r = 1.0f / sqrtf(ss / (float)dv + eps);
-    const float* grow = g + (size_t)t * ldg + (size_t)hh * dv;
+    const float* grow = g ? g + (size_t)t * ldg + (size_t)hh * dv : nullptr;
     for (int i = lane; i < dv; i += 32) {
-        const float gv = grow[i];
         float y = orow[i] * r;
         if (w) y *= w[i];
-        out[(size_t)wi * dv + i] = from_f32<O>(y * (gv / (1.0f + expf(-gv))));
+        if (grow) {
+            const float gv = grow[i];
+            y *= gv / (1.0f + expf(-gv));
+        }
+        out[(size_t)wi * dv + i] = from_f32<O>(y);
     }
 }
 
@@ -597,26 +650,36 @@ extern "C" int aie_gate_group_norm(const float* y, const float* z, int ldz, cons
 // the outputs form `groups` equal groups of neighbours, a group counts as its best member, and only members of the
 // `keep` best groups can be chosen (the others count as minus infinity); the `top` largest are taken, and their
 // weights are their s.  z [T, E] (rows ld floats apart) is replaced by s; scratch [T, E]; ids, weights [T, top].
-// One thread per token.
+// Variants: sigmoid != 0: s = sigmoid(z) per output instead of the softmax; group_top n > 1: a group counts as the sum
+// of its n largest members; normalise != 0: the chosen weights are divided by their sum (+ 1e-20); all weights are
+// multiplied by weight_scale.  One thread per token.
 // ---------------------------------------------------------------------------
 __global__ void route_topk_kernel(float* __restrict__ z, int ld, float* __restrict__ scratch, const float* __restrict__ corr,
                                   int T, int E, int groups, int keep, int top, int* __restrict__ ids,
-                                  float* __restrict__ weights) {
+                                  float* __restrict__ weights, int sigmoid, int group_top, int normalise,
+                                  float weight_scale) {
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= T) return;
     float* s = z + (size_t)t * ld;
     float* c = scratch + (size_t)t * E;
-    float m = -INFINITY;
-    for (int e = 0; e < E; ++e) m = fmaxf(m, s[e]);
-    float sum = 0.f;
-    for (int e = 0; e < E; ++e) {
-        const float v = expf(s[e] - m);
-        s[e] = v;
-        sum += v;
-    }
-    for (int e = 0; e < E; ++e) {
-        s[e] = s[e] / sum;
-        c[e] = s[e] + (corr ? corr[e] : 0.f);
+    if (sigmoid) {
+        for (int e = 0; e < E; ++e) {
+            s[e] = 1.0f / (1.0f + expf(-s[e]));
+            c[e] = s[e] + (corr ? corr[e] : 0.f);
+        }
+    } else {
+        float m = -INFINITY;
+        for (int e = 0; e < E; ++e) m = fmaxf(m, s[e]);
+        float sum = 0.f;
+        for (int e = 0; e < E; ++e) {
+            const float v = expf(s[e] - m);
+            s[e] = v;
+            sum += v;
+        }
+        for (int e = 0; e < E; ++e) {
+            s[e] = s[e] / sum;
+            c[e] = s[e] + (corr ? corr[e] : 0.f);
+        }
     }
     const int per = E / groups;
     if (keep < groups) {
@@ -627,7 +690,28 @@ __global__ void route_topk_kernel(float* __restrict__ z, int ld, float* __restri
             for (int g = 0; g < groups; ++g) {
                 if (kept >> g & 1ull) continue;
                 float gv = -INFINITY;
-                for (int e = g * per; e < (g + 1) * per; ++e) gv = fmaxf(gv, c[e]);
+                if (group_top <= 1) {
+                    for (int e = g * per; e < (g + 1) * per; ++e) gv = fmaxf(gv, c[e]);
+                } else {                                    // the sum of the group's group_top largest members
+                    gv = 0.f;
+                    float bound = INFINITY;                 // members are taken in descending order; ties by index
+                    int bound_e = -1;
+                    for (int n = 0; n < group_top && n < per; ++n) {
+                        float best = -INFINITY;
+                        int best_e = -1;
+                        for (int e = g * per; e < (g + 1) * per; ++e) {
+                            const bool below = c[e] < bound || (c[e] == bound && e > bound_e);
+                            if (below && (best_e < 0 || c[e] > best)) {
+                                best = c[e];
+                                best_e = e;
+                            }
+                        }
+                        if (best_e < 0) break;
+                        gv += best;
+                        bound = best;
+                        bound_e = best_e;
+                    }
+                }
                 if (bg < 0 || gv > bv) {
                     bg = g;
                     bv = gv;
@@ -651,24 +735,36 @@ __global__ void route_topk_kernel(float* __restrict__ z, int ld, float* __restri
         weights[(size_t)t * top + k] = be >= 0 ? s[be] : 0.f;
         if (be >= 0) c[be] = -INFINITY;
     }
+    float div = 1.f;
+    if (normalise) {
+        float sum = 0.f;
+        for (int k = 0; k < top; ++k) sum += weights[(size_t)t * top + k];
+        div = sum + 1e-20f;
+    }
+    if (normalise || weight_scale != 1.f)
+        for (int k = 0; k < top; ++k) weights[(size_t)t * top + k] = weights[(size_t)t * top + k] / div * weight_scale;
 }
 
 extern "C" int aie_route_topk(float* z, int ld, float* scratch, const float* corr, int T, int E, int groups, int keep, int top,
-                              int* ids, float* weights, cudaStream_t st) {
+                              int* ids, float* weights, int sigmoid, int group_top, int normalise, float weight_scale,
+                              cudaStream_t st) {
     if (T <= 0) return 0;
     if (E <= 0 || ld < E || groups <= 0 || E % groups || keep <= 0 || keep > groups || top <= 0 || top > E / groups * keep)
         return AIE_BAD_ARG;
     if (groups > 64) return AIE_UNSUPPORTED;
-    route_topk_kernel<<<(T + 63) / 64, 64, 0, st>>>(z, ld, scratch, corr, T, E, groups, keep, top, ids, weights);
+    route_topk_kernel<<<(T + 63) / 64, 64, 0, st>>>(z, ld, scratch, corr, T, E, groups, keep, top, ids, weights, sigmoid,
+                                                    group_top, normalise, weight_scale);
     AIE_LAUNCH_CHECK();
 }
 
 // out[t] = sum_s weight[t, s] * (row >= 0 ? y[row] : row == -2 ? h[t] : 0),  row = pair_row[t top + s]      float32
-// (a pair marked -2 belongs to an expert that hands its input on unchanged)
+// (a pair marked -2 belongs to an expert that hands its input on unchanged); with `shared` (float32 [parts, T, D], the
+// parts shared_stride floats apart): the sum of its parts is added, an expert that every token uses
 template <typename A>
 __global__ void expert_combine_weighted_kernel(const float* __restrict__ y, const int* __restrict__ pair_row,
                                                const float* __restrict__ weight, int top, const A* __restrict__ h,
-                                               float* __restrict__ out, int D) {
+                                               float* __restrict__ out, int D, const float* __restrict__ shared,
+                                               int shared_parts, size_t shared_stride) {
     const int t = blockIdx.x;
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
         float acc = 0.f;
@@ -678,18 +774,51 @@ __global__ void expert_combine_weighted_kernel(const float* __restrict__ y, cons
             if (row >= 0) acc = fmaf(w, y[(size_t)row * D + c], acc);
             else if (row == -2) acc = fmaf(w, to_f32<A>(h[(size_t)t * D + c]), acc);
         }
+        if (shared) {
+            float sh = 0.f;
+            for (int p = 0; p < shared_parts; ++p) sh += shared[p * shared_stride + (size_t)t * D + c];
+            acc += sh;
+        }
         out[(size_t)t * D + c] = acc;
     }
 }
 
 extern "C" int aie_expert_combine_weighted(const float* y, const int* pair_row, const float* weight, int top,
-                                           const void* h, int h_dtype, float* out, int T, int D, cudaStream_t st) {
+                                           const void* h, int h_dtype, float* out, int T, int D, const float* shared,
+                                           int shared_parts, long long shared_stride, cudaStream_t st) {
     if (T <= 0) return 0;
     if (D <= 0 || top <= 0) return AIE_BAD_ARG;
     const int threads = D >= 1024 ? 256 : 128;
     if (h_dtype == AIE_BF16)
-        expert_combine_weighted_kernel<bf16><<<T, threads, 0, st>>>(y, pair_row, weight, top, (const bf16*)h, out, D);
+        expert_combine_weighted_kernel<bf16><<<T, threads, 0, st>>>(y, pair_row, weight, top, (const bf16*)h, out, D, shared, shared_parts, (size_t)shared_stride);
     else
-        expert_combine_weighted_kernel<float><<<T, threads, 0, st>>>(y, pair_row, weight, top, (const float*)h, out, D);
+        expert_combine_weighted_kernel<float><<<T, threads, 0, st>>>(y, pair_row, weight, top, (const float*)h, out, D, shared, shared_parts, (size_t)shared_stride);
+    AIE_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------
+// RMS norm of a slice of a wider projection: out[t, :] = x[t, :n] / sqrt(mean(x[t, :n]^2) + eps) * w, rows of x
+// `ld` floats apart, float32 statistics.  One block per token.
+// ---------------------------------------------------------------------------
+template <typename O>
+__global__ void slice_rmsnorm_kernel(const float* __restrict__ x, int ld, const float* __restrict__ w, O* __restrict__ out,
+                                     int n, float eps) {
+    __shared__ float red[32];
+    const float* row = x + (size_t)blockIdx.x * ld;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) ss += row[i] * row[i];
+    ss = block_sum(ss, red);
+    const float r = 1.0f / sqrtf(ss / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) out[(size_t)blockIdx.x * n + i] = from_f32<O>((row[i] * r) * w[i]);
+}
+
+extern "C" int aie_slice_rmsnorm(const float* x, int ld, const float* w, void* out, int out_dtype, int T, int n, float eps,
+                                 cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (n <= 0 || ld < n) return AIE_BAD_ARG;
+    const int threads = n >= 1024 ? 256 : 128;
+    if (out_dtype == AIE_F32) slice_rmsnorm_kernel<float><<<T, threads, 0, st>>>(x, ld, w, (float*)out, n, eps);
+    else if (out_dtype == AIE_BF16) slice_rmsnorm_kernel<bf16><<<T, threads, 0, st>>>(x, ld, w, (bf16*)out, n, eps);
+    else return AIE_BAD_ARG;
     AIE_LAUNCH_CHECK();
 }

@@ -10,6 +10,11 @@
 //   sink_attn_prepare    from a step's fused projection [q | k | v | gate logits] (float32): adds the biases,
 //                        writes q in the compute dtype, divides each head's value by its root mean square
 //                        (no weight) and writes key and value into the token's cache row, gate = sigmoid.
+//   normed_attn_prepare  for a layer that norms and rotates instead: from a fused projection whose first columns are
+//                        [q | k | v] it adds the biases, divides all of q (and all of k) by its root mean square
+//                        over the whole projection, times a weight per element, rotates the first rot_dims
+//                        elements of every head (neighbouring pairs, or halves), mixes the value with another
+//                        layer's value of the same token, and writes q and the cache row [k | v].
 //   sink_attention_plain one block per (query token, head), any sizes up to 256; keys are walked in chunks of
 //                        128 that start at multiples of 128 of the absolute key position, so the order of
 //                        every addition depends on the query's position only.
@@ -71,6 +76,112 @@ extern "C" int aie_sink_attn_prepare(const float* proj, int ld, const float* bia
     else if (q_dtype == AIE_BF16) AIE_SAP(bf16);
     else return AIE_BAD_ARG;
 #undef AIE_SAP
+    AIE_LAUNCH_CHECK();
+}
+
+// x [n] holds whole heads of `d` elements; element c after the rotation by `pos` of its head's first rot_dims elements
+__device__ __forceinline__ float head_rotated(const float* x, int c, int d, int rot_dims, int halves, int pos,
+                                              const float* __restrict__ inv_freq) {
+    const int i = c % d;
+    if (i >= rot_dims) return x[c];
+    const int half = rot_dims >> 1;
+    float sn, cs;
+    if (halves) {
+        const int j = i < half ? i : i - half;
+        sincosf((float)pos * inv_freq[j], &sn, &cs);
+        return i < half ? x[c] * cs - x[c + half] * sn : x[c] * cs + x[c - half] * sn;
+    }
+    sincosf((float)pos * inv_freq[i >> 1], &sn, &cs);
+    return (i & 1) ? x[c] * cs + x[c - 1] * sn : x[c] * cs - x[c + 1] * sn;
+}
+
+// proj [T, >= H d + G d + G e] float32; bias [H d + G d + G e] or null; q_w [H d], k_w [G d] float32 or null (no norm).
+// mix_from [T, G e] float32 with lambda (one float on the device): v <- (1 - lambda) v + lambda mix_from[t].
+// v_keep [T, G e]: receives v as it is cached, in float32 (for the layers that mix with it).
+template <typename A>
+__global__ void __launch_bounds__(256)
+normed_attn_prepare_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ bias,
+                           const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+                           const float* __restrict__ inv_freq, int rot_dims, int halves,
+                           const float* __restrict__ mix_from, const float* __restrict__ lambda,
+                           float* __restrict__ v_keep, A* __restrict__ q_out, A* __restrict__ pages,
+                           const int* __restrict__ positions, const int* __restrict__ token_req,
+                           const int* __restrict__ block_table, int bt_width, int num_pages, int P, int H, int G, int d,
+                           int e, int write, unsigned* err) {
+    extern __shared__ __align__(16) float np_sm[];     // q (H d) | k (G d) | 32
+    const int t = blockIdx.x, tid = threadIdx.x;
+    const int nq = H * d, nk = G * d, nv = G * e;
+    float* qs = np_sm;
+    float* ks = qs + nq;
+    float* red = ks + nk;
+    const float* row = proj + (size_t)t * ld;
+    float ssq = 0.f, ssk = 0.f;
+    for (int c = tid; c < nq; c += blockDim.x) {
+        const float x = row[c] + (bias ? bias[c] : 0.f);
+        qs[c] = x;
+        ssq += x * x;
+    }
+    for (int c = tid; c < nk; c += blockDim.x) {
+        const float x = row[nq + c] + (bias ? bias[nq + c] : 0.f);
+        ks[c] = x;
+        ssk += x * x;
+    }
+    ssq = block_sum(ssq, red);
+    ssk = block_sum(ssk, red);
+    if (q_w) {
+        const float rq = 1.0f / sqrtf(ssq / (float)nq + eps), rk = 1.0f / sqrtf(ssk / (float)nk + eps);
+        for (int c = tid; c < nq; c += blockDim.x) qs[c] = (qs[c] * rq) * q_w[c];
+        for (int c = tid; c < nk; c += blockDim.x) ks[c] = (ks[c] * rk) * k_w[c];
+    }
+    __syncthreads();
+    const int pos = positions[t];
+    for (int c = tid; c < nq; c += blockDim.x)
+        q_out[(size_t)t * nq + c] = from_f32<A>(rot_dims > 0 ? head_rotated(qs, c, d, rot_dims, halves, pos, inv_freq) : qs[c]);
+    const int pidx = pos / P;
+    const int page = (pos >= 0 && pidx < bt_width) ? block_table[(size_t)token_req[t] * bt_width + pidx] : -1;
+    const bool page_ok = page >= 0 && page < num_pages;
+    if (write && !page_ok && tid == 0) atomicOr(err, AIE_DEV_PAGE_OOB);
+    const int w = d + e;
+    A* base = pages + ((size_t)(page_ok ? page : 0) * G * P + (pos % P)) * w;
+    if (write && page_ok)
+        for (int c = tid; c < nk; c += blockDim.x) {
+            const int g = c / d;
+            base[(size_t)g * P * w + (c - g * d)] =
+                from_f32<A>(rot_dims > 0 ? head_rotated(ks, c, d, rot_dims, halves, pos, inv_freq) : ks[c]);
+        }
+    const float lam = mix_from ? lambda[0] : 0.f;
+    for (int c = tid; c < nv; c += blockDim.x) {
+        float v = row[nq + nk + c] + (bias ? bias[nq + nk + c] : 0.f);
+        if (mix_from) v = (1.0f - lam) * v + lam * mix_from[(size_t)t * nv + c];
+        if (v_keep) v_keep[(size_t)t * nv + c] = v;
+        if (write && page_ok) {
+            const int g = c / e;
+            base[(size_t)g * P * w + d + (c - g * e)] = from_f32<A>(v);
+        }
+    }
+}
+
+extern "C" int aie_normed_attn_prepare(const float* proj, int ld, const float* bias, const float* q_w, const float* k_w,
+                                       float eps, const float* inv_freq, int rot_dims, int halves, const float* mix_from,
+                                       const float* lambda, float* v_keep, void* q_out, void* pages, int dtype,
+                                       const int* positions, const int* token_req, const int* block_table, int bt_width,
+                                       int num_pages, int P, int T, int H, int G, int d, int e, int write, unsigned* err,
+                                       cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || G <= 0 || H % G || d <= 0 || e <= 0 || rot_dims < 0 || rot_dims > d || rot_dims % 2 ||
+        (mix_from && !lambda) || (q_w && !k_w) || (rot_dims > 0 && !inv_freq))
+        return AIE_BAD_ARG;
+    const size_t smem = ((size_t)(H + G) * d + 32) * sizeof(float);
+    if (smem > 48 * 1024) return AIE_UNSUPPORTED;
+#define AIE_NAP(A)                                                                                                    \
+    normed_attn_prepare_kernel<A><<<T, 256, smem, stream>>>(proj, ld, bias, q_w, k_w, eps, inv_freq, rot_dims, halves, \
+                                                           mix_from, lambda, v_keep, (A*)q_out, (A*)pages, positions, \
+                                                           token_req, block_table, bt_width, num_pages, P, H, G, d, e, \
+                                                           write, err)
+    if (dtype == AIE_F32) AIE_NAP(float);
+    else if (dtype == AIE_BF16) AIE_NAP(bf16);
+    else return AIE_BAD_ARG;
+#undef AIE_NAP
     AIE_LAUNCH_CHECK();
 }
 

@@ -660,18 +660,19 @@ def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float, out_dtype: torch.d
     return out
 
 
-def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.Tensor], eps: float,
+def head_norm_gate(o: torch.Tensor, gate: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float,
                    out_dtype: torch.dtype) -> torch.Tensor:
-    """Per (token, head): o / rms(o) (* weight) * silu(gate).  o [T, H, dv] float32; gate [T, H * dv] float32,
-    rows gate.stride(0) apart; weight [dv] float32 or None.  Returns [T, H * dv]."""
+    """Per (token, head): o / rms(o) (* weight) (* silu(gate)).  o [T, H, dv] float32; gate [T, H * dv] float32,
+    rows gate.stride(0) apart, or None (no gate); weight [dv] float32 or None.  Returns [T, H * dv]."""
     _dev(o, weight)
     T, H, dv = o.shape
-    if o.dtype != torch.float32 or gate.dtype != torch.float32 or gate.stride(1) != 1 or gate.shape != (T, H * dv):
+    if o.dtype != torch.float32 or (gate is not None and (gate.dtype != torch.float32 or gate.stride(1) != 1
+                                                          or gate.shape != (T, H * dv))):
         raise KernelError("head_norm_gate: shapes or dtypes do not fit")
     out = torch.empty((T, H * dv), dtype=out_dtype, device=o.device)
     lib = library("sequence_ops.cu")
     with region("head_norm_gate", 2 * _nb(o) + _nb(out)):
-        check(lib.aie_head_norm_gate(_p(o), _p(gate), c_int(gate.stride(0)), _p(weight), _p(out),
+        check(lib.aie_head_norm_gate(_p(o), _p(gate), c_int(gate.stride(0) if gate is not None else 0), _p(weight), _p(out),
                                      c_int(dtype_code(out)), c_int(T), c_int(H), c_int(dv), c_float(eps), _stream()),
               "head_norm_gate")
     return out
@@ -748,14 +749,18 @@ def expert_combine(y: torch.Tensor, pair_row: torch.Tensor, top: int, weight: fl
 
 def latent_prepare(proj: torch.Tensor, H: int, d: int, rot: int, rank: int, c_weight: Optional[torch.Tensor],
                    eps: float, inv_freq: torch.Tensor, pages: torch.Tensor, ctx, block_table: torch.Tensor,
-                   q_dtype: torch.dtype, write: bool):
+                   q_dtype: torch.dtype, write: bool, kv: Optional[torch.Tensor] = None, halves: bool = False):
     """From the fused projection [q heads (d plain | rot rotated) | latent (rank) | shared key part (rot)] of a
     step: (q_plain [T, H, d] in q_dtype, q_full [T, H, rank + rot] float32 whose last rot columns hold the
     rotated query parts); with `write`, the normalised latent and the rotated key part go into the tokens'
-    cache rows.  pages [num_pages, 1, P, rank + rot]."""
+    cache rows.  pages [num_pages, 1, P, rank + rot].  kv: the latent and the key part come from this float32 view
+    [T, >= rank + rot] (rows any stride) instead of the columns behind the queries.  halves: the rotation pairs
+    element i with i + rot_dims / 2 instead of 2i with 2i + 1."""
     _dev(proj, c_weight, inv_freq, pages, block_table)
     T, ld = proj.shape
-    need = H * (d + rot) + ((rank + rot) if write else 0)
+    need = H * (d + rot) + ((rank + rot) if write and kv is None else 0)
+    if kv is not None and (kv.dtype != torch.float32 or kv.stride(1) != 1 or kv.shape[0] != T or kv.shape[1] < rank + rot):
+        raise KernelError("latent_prepare: the latent projection is a float32 view [T, >= rank + rot]")
     if proj.dtype != torch.float32 or ld < need or pages.shape[1] != 1 or pages.shape[3] != rank + rot:
         raise KernelError("latent_prepare: shapes or dtypes do not fit")
     q_plain = torch.empty((T, H, d), dtype=q_dtype, device=proj.device)
@@ -767,7 +772,8 @@ def latent_prepare(proj: torch.Tensor, H: int, d: int, rot: int, rank: int, c_we
                                      c_float(eps), _p(inv_freq), _p(q_plain), c_int(dtype_code(q_plain)), _p(q_full),
                                      _p(pages), c_int(dtype_code(pages)), _p(ctx.positions), _p(ctx.token_req),
                                      _p(block_table), c_int(block_table.shape[1]), c_int(pages.shape[0]),
-                                     c_int(pages.shape[2]), _p(ctx.err), _stream()), "latent_prepare")
+                                     c_int(pages.shape[2]), _p(ctx.err), _p(kv), c_int(kv.stride(0) if kv is not None else 0),
+                                     c_int(1 if halves else 0), _stream()), "latent_prepare")
     return q_plain, q_full
 
 
@@ -830,7 +836,8 @@ def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_t
                       decay_head: Optional[torch.Tensor], q_scale: float, k_scale: float, state: torch.Tensor,
                       ctx, H: int, d: int, dv: int, heads_per_group: int = 1, dt_raw: Optional[torch.Tensor] = None,
                       dt_bias: Optional[torch.Tensor] = None, a_log: Optional[torch.Tensor] = None,
-                      skip: Optional[torch.Tensor] = None, chunked: bool = False, wide_state: bool = False) -> torch.Tensor:
+                      skip: Optional[torch.Tensor] = None, chunked: bool = False, wide_state: bool = False,
+                      forget_lower: Optional[torch.Tensor] = None, forget_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """S <- diag(a_t) S + k_t v_t^T, o_t = S^T q_t per request and head over the step's tokens, the state
     [max_seqs, H, d, dv] float32 read and left in each request's slot.  q, k [T, H * d] and v [T, H * dv] are
     float32 views with one row stride; decay_tok [T, H * d] float32 (rows any stride) or decay_head [H].
@@ -841,8 +848,14 @@ def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_t
     take the chunked tensor-core kernel, which rounds q, k and v to bfloat16 (a state of up to 128 rows).
     wide_state (with dt_raw): step sizes, decays and a step's updates are made in double and the state is rounded
     once, when it returns to its float32 slot.
+    forget_lower [H * d] float32 (with forget_bias [H * d] or None): the keyless form.  k is None, decay_tok holds the
+    forget gate's logits z, and the kernel makes a = l + (1 - l) sigmoid(z + bias), k = 1 - a and q = silu(q) itself.
     Returns o [T, H, dv] float32."""
-    _dev(state, decay_head, dt_bias, a_log, skip)
+    _dev(state, decay_head, dt_bias, a_log, skip, forget_lower, forget_bias)
+    if forget_lower is not None:
+        if k is not None or decay_tok is None or forget_lower.dtype != torch.float32 or forget_lower.numel() != H * d:
+            raise KernelError("linear_recurrence: the keyless form takes the gate's logits as decay_tok and no keys")
+        k = q                    # stands in for the shape checks below; the kernel gets no keys
     if dt_raw is not None and (dt_raw.dtype != torch.float32 or dt_raw.stride(1) != 1 or dt_bias is None or a_log is None):
         raise KernelError("linear_recurrence: step sizes are a float32 view with their bias and rates")
     T = q.shape[0]
@@ -867,13 +880,14 @@ def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_t
         max_len = SSD_MIN_TOKENS - 1                # the shorter portions and single tokens of the same step
     lib = library("linear_recurrence.cu")
     with region("linear_recurrence", _nb(out) + T * H * (2 * d + dv) * 4 + 2 * ctx.R * H * d * dv * 4, 4.0 * T * H * d * dv):
-        check(lib.aie_linear_recurrence(_p(q), _p(k), _p(v), c_int(ld), _p(decay_tok),
+        check(lib.aie_linear_recurrence(_p(q), _p(None if forget_lower is not None else k), _p(v), c_int(ld), _p(decay_tok),
                                         c_int(decay_tok.stride(0) if decay_tok is not None else 0), _p(decay_head),
                                         c_float(q_scale), c_float(k_scale), _p(state), _p(out), _p(ctx.q_start),
                                         _p(ctx.q_len), _p(ctx.slots), c_int(T), c_int(ctx.R), c_int(H), c_int(d), c_int(dv),
                                         c_int(state.shape[0]), _p(ctx.err), c_int(heads_per_group), _p(dt_raw),
                                         c_int(dt_raw.stride(0) if dt_raw is not None else 0), _p(dt_bias), _p(a_log),
-                                        _p(skip), c_int(max_len), c_int(1 if wide_state else 0), _stream()),
+                                        _p(skip), c_int(max_len), c_int(1 if wide_state else 0), _p(forget_lower),
+                                        _p(forget_bias), _stream()),
               "linear_recurrence")
     return out
 
@@ -958,11 +972,14 @@ def gate_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, part
     return out
 
 
-def route_topk(logits: torch.Tensor, correction: Optional[torch.Tensor], groups: int, keep: int, top: int):
+def route_topk(logits: torch.Tensor, correction: Optional[torch.Tensor], groups: int, keep: int, top: int,
+               score: str = "softmax", group_top: int = 1, normalise: bool = False, weight_scale: float = 1.0):
     """A router's choice per token from float32 logits [T, E] (a view whose rows may be wider apart; overwritten by their softmax): the `top` outputs
     with the largest softmax + correction among the members of the `keep` groups (of `groups` equal groups of
     neighbours) whose best member is largest.  Returns (ids int32 [T, top], weights float32 [T, top]: the
-    chosen outputs' softmax)."""
+    chosen outputs' softmax).  score "sigmoid": every output's score is its own sigmoid instead.  group_top n: a group
+    counts as the sum of its n largest members.  normalise: the chosen weights are divided by their sum (+ 1e-20);
+    weight_scale multiplies them."""
     _dev(correction)
     T, E = logits.shape
     if logits.dtype != torch.float32 or logits.stride(1) != 1 or (correction is not None and (correction.dtype != torch.float32 or
@@ -974,14 +991,20 @@ def route_topk(logits: torch.Tensor, correction: Optional[torch.Tensor], groups:
     lib = library("sequence_ops.cu")
     with region("route_topk", 3 * _nb(scratch)):
         check(lib.aie_route_topk(_p(logits), c_int(logits.stride(0)), _p(scratch), _p(correction), c_int(T), c_int(E), c_int(groups), c_int(keep),
-                                 c_int(top), _p(ids), _p(weights), _stream()), "route_topk")
+                                 c_int(top), _p(ids), _p(weights), c_int(1 if score == "sigmoid" else 0), c_int(group_top),
+                                 c_int(1 if normalise else 0), c_float(weight_scale), _stream()), "route_topk")
     return ids, weights
 
 
-def expert_combine_weighted(y: torch.Tensor, pair_row: torch.Tensor, weights: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
-    """out[t] = sum_s weights[t, s] * y[pair_row[t top + s]], a pair marked -2 standing for h[t] itself; float32
-    [T, D].  y [rows, D] float32; weights [T, top] float32; h [T, D] in the compute dtype."""
-    _dev(y, pair_row, weights, h)
+def expert_combine_weighted(y: torch.Tensor, pair_row: torch.Tensor, weights: torch.Tensor, h: torch.Tensor,
+                            shared: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = sum_s weights[t, s] * y[pair_row[t top + s]] (+ shared[t]), a pair marked -2 standing for h[t] itself;
+    float32 [T, D].  y [rows, D] float32; weights [T, top] float32; h [T, D] in the compute dtype; shared float32
+    [T, D] or [parts, T, D] (the unjoined parts of a split product, added here)."""
+    _dev(y, pair_row, weights, h, shared)
+    if shared is not None and (shared.dtype != torch.float32 or shared.shape[-2:] != h.shape):
+        raise KernelError("expert_combine_weighted: the shared output is float32 [T, D] or [parts, T, D]")
+    sh_parts, sh_stride = (0, 0) if shared is None else ((shared.shape[0], shared.stride(0)) if shared.dim() == 3 else (1, 0))
     T, top = weights.shape
     D = h.shape[1]
     if y.dtype != torch.float32 or weights.dtype != torch.float32 or y.shape[1] != D or pair_row.numel() != T * top:
@@ -990,7 +1013,8 @@ def expert_combine_weighted(y: torch.Tensor, pair_row: torch.Tensor, weights: to
     lib = library("sequence_ops.cu")
     with region("expert_combine", (top + 2) * T * D * 4):
         check(lib.aie_expert_combine_weighted(_p(y), _p(pair_row), _p(weights), c_int(top), _p(h), c_int(dtype_code(h)),
-                                              _p(out), c_int(T), c_int(D), _stream()), "expert_combine_weighted")
+                                              _p(out), c_int(T), c_int(D), _p(shared), c_int(sh_parts),
+                                              c_longlong(sh_stride), _stream()), "expert_combine_weighted")
     return out
 
 
@@ -1218,4 +1242,147 @@ def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, b_raw: torch.T
                                  _p(state), _p(out), _p(ctx.q_start), _p(ctx.q_len), _p(ctx.slots), _p(ctx.live),
                                  c_int(ctx.R), c_int(H), c_int(G), c_int(d), c_int(e), c_int(state.shape[0]),
                                  c_int(max_len), _p(ctx.err), _stream()), "delta_rule")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# parts of layers whose sublayers run side by side behind a norm without statistics, attention with normed and
+# rotated heads whose values are mixed across layers, gates on attention outputs
+def add_dyt(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, bias: torch.Tensor, alpha: torch.Tensor,
+            out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None, write_back: bool = True) -> torch.Tensor:
+    """s = x (+ delta, or the sum of its parts [parts, T, D]); out = tanh(alpha s) * weight + bias, element by element
+    in float32.  x is the float32 residual stream and receives s when `write_back`; `rows` picks rows; weight, bias
+    [D] and alpha [1] are float32 on the device."""
+    _dev(x, delta, weight, bias, alpha, rows)
+    D = x.shape[-1]
+    if x.dtype != torch.float32 or any(t.dtype != torch.float32 for t in (weight, bias, alpha)):
+        raise KernelError("add_dyt: the stream and the norm's tensors are float32")
+    if weight.shape != (D,) or bias.shape != (D,) or alpha.numel() != 1:
+        raise KernelError("add_dyt: weight and bias [D], alpha one number")
+    parts, stride = 0, 0
+    if delta is not None:
+        parts, stride = (delta.shape[0], delta.stride(0)) if delta.dim() == 3 else (1, 0)
+        if delta.shape[-2:] != x.shape:
+            raise KernelError("add_dyt: delta differs in shape from x")
+    n = x.shape[0] if rows is None else rows.shape[0]
+    out = torch.empty((n, D), dtype=out_dtype, device=x.device)
+    stored = write_back and rows is None and delta is not None
+    lib = library("elementwise.cu")
+    with region("add_dyt", n * D * 4 * (2 if stored else 1) + (_nb(delta) if rows is None else 0) + _nb(out)):
+        check(lib.aie_add_dyt(_p(x), _p(delta), c_int(dtype_code(delta) if delta is not None else 0), c_int(parts),
+                              c_longlong(stride), _p(weight), _p(bias), _p(alpha), _p(out), c_int(dtype_code(out)), _p(rows),
+                              c_int(n), c_int(D), c_int(1 if stored else 0), _stream()), "add_dyt")
+    return out
+
+
+def sigmoid_gate_mul_(a: torch.Tensor, g: torch.Tensor, group: int = 1) -> torch.Tensor:
+    """a[t, n] <- a[t, n] * sigmoid(g[t, n / group]) in place.  a [T, N] (float32 or bfloat16); g a float32 view
+    [T, N / group] with any row stride.  group 1: a gate per element; group = a head's width: a gate per head."""
+    _dev(a)
+    T, N = a.shape
+    if g.dtype != torch.float32 or g.stride(1) != 1 or N % group or g.shape != (T, N // group):
+        raise KernelError("sigmoid_gate_mul: the gate's logits are a float32 view [T, N / group]")
+    lib = library("elementwise.cu")
+    with region("sigmoid_gate_mul", 2 * _nb(a) + T * (N // group) * 4):
+        check(lib.aie_sigmoid_gate_mul(_p(a), c_int(dtype_code(a)), _p(g), c_int(g.stride(0)), c_int(T), c_int(N), c_int(group),
+                                       _stream()), "sigmoid_gate_mul")
+    return a
+
+
+def add_bias_(y: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """y[..., n] += bias[n] in place; y float32 [T, N], or [parts, T, N] (the bias joins the first part)."""
+    _dev(y, bias)
+    N = y.shape[-1]
+    if y.dtype != torch.float32 or bias.dtype != torch.float32 or bias.shape != (N,):
+        raise KernelError("add_bias: float32 operands, one bias per column")
+    first = y[0] if y.dim() == 3 else y
+    lib = library("elementwise.cu")
+    with region("add_bias", 2 * _nb(first)):
+        check(lib.aie_add_bias(_p(first), _p(bias), c_int(first.shape[0]), c_int(N), _stream()), "add_bias")
+    return y
+
+
+def _parts_of(t: Optional[torch.Tensor], shape):
+    if t is None:
+        return 0, 0
+    if t.dtype != torch.float32 or t.shape[-2:] != shape:
+        raise KernelError("a branch output is float32 [T, D] or [parts, T, D]")
+    return (t.shape[0], t.stride(0)) if t.dim() == 3 else (1, 0)
+
+
+def parallel_residual(x: torch.Tensor, a: torch.Tensor, b: Optional[torch.Tensor], mult: float,
+                      history: Optional[torch.Tensor] = None, coef: Optional[torch.Tensor] = None, depth: int = 0,
+                      norm_ahead=None, out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """X = x + mult * (a + b) for two branches that read the same input (float32 [T, D] or the unjoined parts
+    [parts, T, D] of a split product; b may be None).  With `coef` (float32 [>= depth + 1]) and `history`
+    [levels, T, D]: history[depth] = X and x = sum_{j <= depth} coef[j] history[j]; otherwise x = X.  In place.
+    norm_ahead = (weight, bias, alpha) of a norm without statistics: also returns tanh(alpha x) weight + bias of the
+    new stream in `out_dtype`, so that whoever norms the stream next need not read it again."""
+    _dev(x, a, b, history, coef)
+    if x.dtype != torch.float32:
+        raise KernelError("parallel_residual: the stream is float32")
+    pa, sa = _parts_of(a, x.shape)
+    pb, sb = _parts_of(b, x.shape)
+    if coef is not None and (history is None or history.shape[1:] != x.shape or depth >= history.shape[0]
+                             or coef.shape[0] < depth + 1 or coef.dtype != torch.float32):
+        raise KernelError("parallel_residual: history and weights do not fit")
+    normed = None
+    w = nb = al = None
+    if norm_ahead is not None:
+        w, nb, al = norm_ahead
+        normed = torch.empty(x.shape, dtype=out_dtype or torch.float32, device=x.device)
+    lib = library("sequence_ops.cu")
+    with region("parallel_residual", ((depth + 3) if coef is not None else 2) * _nb(x) + _nb(a, b, normed)):
+        check(lib.aie_depth_average2(_p(x), _p(a), c_int(pa), c_longlong(sa), _p(b), c_int(pb), c_longlong(sb), c_float(mult),
+                                     _p(history), _p(coef), c_int(depth), c_longlong(x.numel()), _p(w), _p(nb), _p(al),
+                                     _p(normed), c_int(dtype_code(normed) if normed is not None else 0),
+                                     c_int(x.shape[-1]), _stream()), "parallel_residual")
+    return normed
+
+
+def normed_attn_prepare(proj: torch.Tensor, bias: Optional[torch.Tensor], q_weight: Optional[torch.Tensor],
+                        k_weight: Optional[torch.Tensor], eps: float, inv_freq: Optional[torch.Tensor], rot_dims: int,
+                        halves: bool, pages: torch.Tensor, ctx, block_table: torch.Tensor, H: int, G: int, d: int, e: int,
+                        mix_from: Optional[torch.Tensor] = None, mix_lambda: Optional[torch.Tensor] = None,
+                        keep_values: bool = False, write: bool = True):
+    """From a step's fused projection whose first columns are [q (H d) | k (G d) | v (G e)] (float32 [T, >= that]):
+    biases added; all of q divided by its root mean square over the H d elements, times q_weight (k likewise; None: no
+    norm); the first rot_dims elements of every head of q and k rotated by the token's position (pairs of neighbours,
+    or halves); v <- (1 - lambda) v + lambda mix_from[t] when mix_from [T, G e] float32 is given (lambda one float on
+    the device).  q [T, H, d] in the cache's dtype is returned; with `write`, the token's cache row [k | v] is
+    written.  keep_values: the values as they are cached are also returned in float32 [T, G e].
+    pages [num_pages, G, P, d + e]."""
+    _dev(proj, bias, q_weight, k_weight, inv_freq, pages, block_table, mix_from, mix_lambda)
+    T, ld = proj.shape
+    n = H * d + G * (d + e)
+    if (proj.dtype != torch.float32 or ld < n or pages.shape[1] != G or pages.shape[3] != d + e
+            or (bias is not None and (bias.dtype != torch.float32 or bias.numel() != n))
+            or (q_weight is not None and (k_weight is None or q_weight.numel() != H * d or k_weight.numel() != G * d))
+            or (mix_from is not None and (mix_from.dtype != torch.float32 or mix_from.shape != (T, G * e) or mix_lambda is None))):
+        raise KernelError("normed_attn_prepare: shapes or dtypes do not fit")
+    q = torch.empty((T, H, d), dtype=pages.dtype, device=proj.device)
+    kept = torch.empty((T, G * e), dtype=torch.float32, device=proj.device) if keep_values else None
+    lib = library("sink_attention.cu")
+    with region("normed_attn_prepare", T * n * 4 + _nb(q, kept, mix_from) + T * G * (d + e) * pages.element_size()):
+        check(lib.aie_normed_attn_prepare(_p(proj), c_int(ld), _p(bias), _p(q_weight), _p(k_weight), c_float(eps),
+                                          _p(inv_freq), c_int(rot_dims), c_int(1 if halves else 0), _p(mix_from),
+                                          _p(mix_lambda), _p(kept), _p(q), _p(pages), c_int(dtype_code(pages)),
+                                          _p(ctx.positions), _p(ctx.token_req), _p(block_table), c_int(block_table.shape[1]),
+                                          c_int(pages.shape[0]), c_int(pages.shape[2]), c_int(T), c_int(H), c_int(G), c_int(d),
+                                          c_int(e), c_int(1 if write else 0), _p(ctx.err), _stream()), "normed_attn_prepare")
+    return q, kept
+
+
+def slice_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """out[t] = x[t] / sqrt(mean(x[t]^2) + eps) * weight for a float32 view x [T, n] with any row stride (a slice of
+    a wider projection); weight [n] float32."""
+    _dev(weight)
+    T, n = x.shape
+    if x.dtype != torch.float32 or x.stride(1) != 1 or weight.dtype != torch.float32 or weight.shape != (n,):
+        raise KernelError("slice_rmsnorm: a float32 view and one float32 weight per column")
+    out = torch.empty((T, n), dtype=out_dtype, device=x.device)
+    lib = library("sequence_ops.cu")
+    with region("slice_rmsnorm", T * n * 4 + _nb(out)):
+        check(lib.aie_slice_rmsnorm(_p(x), c_int(x.stride(0)), _p(weight), _p(out), c_int(dtype_code(out)), c_int(T), c_int(n),
+                                    c_float(eps), _stream()), "slice_rmsnorm")
     return out

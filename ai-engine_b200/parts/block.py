@@ -164,3 +164,69 @@ class SandwichNormBlock(Block):
             h = self.p["ffn_norm"].forward(x, pending)
             pending = self._normed(self.p["ffn_post_norm"], ffn.forward(h, ctx))
         return x, pending
+
+
+class ParallelBlock(Block):
+    """A block whose mixer and feed-forward read the same normed input and are added together:
+
+        h = norm(x);   X = x + mult * (mixer(h) + ffn(h))                                 -> X_(depth + 1)
+        x = sum_{j = 0 .. depth + 1} coef[j] * X_j        (X_0: the stream the first layer received)
+
+    The feed-forward is optional, and so is the averaging (no tensor `coef`: x = X).  params: mult (default 1),
+    depth (number of layers before this one), levels (layers of the model + 1).  tensors: coef [depth + 2].
+    The two branch outputs, the stream and the earlier streams meet in one kernel.  `norm_ahead` (set by the model
+    builder's order of layers through `set_next_norm`): when the norm that reads the stream next is one without
+    statistics, that kernel writes its output too and hangs it on the step for the next block to pick up."""
+
+    roles = {"norm": "norm", "mixer": "mixer", "ffn": "feed_forward"}
+    optional_roles = ("ffn",)
+
+    def __init__(self, spec, env, parts):
+        super().__init__(spec, env)
+        self.norm, self.mixer, self.ffn = parts["norm"], parts["mixer"], parts.get("ffn")
+        self.mult = float(spec.params.get("mult", 1.0))
+        self.depth, self.levels = int(spec.params.get("depth") or 0), int(spec.params.get("levels") or 0)
+        self.coef = None
+        self.next_norm = None
+
+    def tensor_specs(self):
+        name = self.spec.tensors.get("coef")
+        n = self.depth + 2
+        return [TensorSpec(name, (n,), mean=1.0 / n, std=0.1 / n)] if name else []
+
+    def load(self, source):
+        name = self.spec.tensors.get("coef")
+        if name:
+            self.coef = source.get(name).float().contiguous()
+
+    def first_norm(self):
+        return self.norm
+
+    def set_next_norm(self, norm) -> None:
+        """The norm that reads the stream after this block (the next block's, or the model's last); used only if it
+        can be made ahead (`ahead()`) and hands on the compute dtype."""
+        self.next_norm = norm if hasattr(norm, "ahead") else None
+
+    def forward(self, x, pending, ctx, caches):
+        ahead = getattr(ctx, "normed_ahead", None)
+        if pending is None and ahead is not None and ahead[0] is self.norm:
+            h = ahead[1]
+        else:
+            h = self.norm.forward(x, pending)
+        ctx.normed_ahead = None
+        history = None
+        if self.coef is not None:
+            if self.depth == 0:
+                ctx.depth_history = torch.empty((self.levels,) + tuple(x.shape), dtype=torch.float32, device=x.device)
+                ctx.depth_history[0].copy_(x)
+            history = ctx.depth_history
+        a = self.mixer.forward(h, ctx, caches.get("mixer"))
+        b = self.ffn.forward(h, ctx) if self.ffn is not None else None
+        a, b = ops.cast(a, torch.float32), (ops.cast(b, torch.float32) if b is not None else None)
+        nxt = self.next_norm
+        made = ops.parallel_residual(x, a, b, self.mult, history, self.coef, self.depth + 1,
+                                     norm_ahead=nxt.ahead() if nxt is not None else None,
+                                     out_dtype=nxt.out_dtype if nxt is not None else None)
+        if made is not None:
+            ctx.normed_ahead = (nxt, made)
+        return x, None

@@ -10,6 +10,10 @@ qa_h . c = q_plain,h . W_uk,h c) and W_uv is applied to the attention-weighted s
 (sum_j p_j W_uv c_j = W_uv sum_j p_j c_j).  The attention kernel then reads the cache rows as they are, as
 one key/value head for all query heads, for prompts and decoded tokens alike.
 
+The queries may go through a latent of their own (`q_rank`): c_q = RMSnorm(W_dq h) with a weight, q = W_uq c_q.  A
+gate per head (`head_gate`) multiplies head h's output by sigmoid(W_g h)_h; it is applied to the head's values before
+the output projection.  The rotation pairs neighbours or halves, as its encoding says.
+
 A layer may read another layer's cache (`shares_cache`): it has no latent projection of its own and writes
 nothing; the run order names the layer whose rows it reads.
 """
@@ -42,9 +46,11 @@ LATENT_WORK = LatentWork()
 class LatentAttention(Mixer):
     """params: hidden_size, num_heads, head_dim (unrotated part), rot_dim, value_dim, kv_rank, scale, window
     (0 = all keys), cache_window (the window the cached rows must outlive: the widest of all layers that read
-    them; default = window), eps (of the latent's norm), position_encoding (name of an interleaved rotary
-    encoding over rot_dim or fewer elements), shares_cache.  tensors: q [H (d + rot), hidden], dkv [kv_rank +
-    rot, hidden], dkv_norm [kv_rank], uk [H d, kv_rank], uv [H dv, kv_rank], o [hidden, H dv]."""
+    them; default = window), eps (of the latents' norms), position_encoding (name of a rotary encoding over rot_dim
+    or fewer elements, either layout), shares_cache, q_rank (0: the queries are projected directly), head_gate.
+    tensors: q [H (d + rot), hidden] (or, with q_rank: dq [q_rank, hidden], dq_norm [q_rank], uq [H (d + rot),
+    q_rank]), dkv [kv_rank + rot, hidden], dkv_norm [kv_rank], uk [H d, kv_rank], uv [H dv, kv_rank], o [hidden,
+    H dv], g [H, hidden]."""
 
     adds_in_place = True
 
@@ -60,16 +66,24 @@ class LatentAttention(Mixer):
         self.shares_cache = bool(p.get("shares_cache"))
         pe = p.get("position_encoding")
         self.rope = env.position_encodings[pe] if pe else None
-        if self.rope is not None:
-            if not getattr(self.rope, "interleaved", False):
-                raise ValueError("latent attention rotates interleaved pairs: its encoding needs layout=interleaved")
-            if self.rope.rot_dim > self.rot:
-                raise ValueError("latent attention: the rotation is wider than rot_dim")
+        if self.rope is not None and self.rope.rot_dim > self.rot:
+            raise ValueError("latent attention: the rotation is wider than rot_dim")
+        self.halves = self.rope is not None and not getattr(self.rope, "interleaved", False)
+        self.q_rank, self.head_gate = int(p.get("q_rank") or 0), bool(p.get("head_gate"))
+        if (self.q_rank or self.head_gate) and self.shares_cache:
+            raise ValueError("latent attention: a layer that reads another's cache has neither a query latent nor a gate")
+        self.w_uq = self.cq_weight = None
         self.w_in = self.w_ukT = self.w_uv = self.w_o = self.c_weight = self._no_rope = None
 
     def tensor_specs(self):
         t, dq = self.spec.tensors, self.d + self.rot
-        specs = [TensorSpec(t["q"], (self.H * dq, self.hidden))]
+        if self.q_rank:
+            specs = [TensorSpec(t["dq"], (self.q_rank, self.hidden)), TensorSpec(t["dq_norm"], (self.q_rank,), init="ones"),
+                     TensorSpec(t["uq"], (self.H * dq, self.q_rank))]
+        else:
+            specs = [TensorSpec(t["q"], (self.H * dq, self.hidden))]
+        if self.head_gate:
+            specs.append(TensorSpec(t["g"], (self.H, self.hidden)))
         if not self.shares_cache:
             specs += [TensorSpec(t["dkv"], (self.rank + self.rot, self.hidden)),
                       TensorSpec(t["dkv_norm"], (self.rank,), init="ones")]
@@ -79,13 +93,20 @@ class LatentAttention(Mixer):
 
     def load(self, source):
         t = self.spec.tensors
-        q = source.get(t["q"])
+        q = source.get(t["dq"] if self.q_rank else t["q"])
+        if self.q_rank:
+            self.w_uq = source.get(t["uq"])
+            self.cq_weight = source.get(t["dq_norm"]).float().contiguous()
         if self.shares_cache:
             self.w_in = q
         else:
-            dkv = source.get(t["dkv"])
-            dt = torch.float32 if torch.float32 in (q.dtype, dkv.dtype) else q.dtype
-            self.w_in = torch.cat([q.to(dt), dkv.to(dt)], dim=0).contiguous()
+            # one product for everything that reads h: [q or its latent | latent | key part | gate logits]
+            ws = [q, source.get(t["dkv"])] + ([source.get(t["g"])] if self.head_gate else [])
+            dt = torch.float32 if any(w.dtype == torch.float32 for w in ws) else q.dtype
+            pad = (-sum(w.shape[0] for w in ws)) % 8     # rows of the product's output stay 16 bytes apart
+            if pad:
+                ws.append(torch.zeros((pad, self.hidden), dtype=dt, device=q.device))
+            self.w_in = torch.cat([w.to(dt) for w in ws], dim=0).contiguous()
             self.c_weight = source.get(t["dkv_norm"]).float().contiguous()
         # [H, kv_rank, d]: the folding product reads W_uk,h transposed
         self.w_ukT = source.get(t["uk"]).view(self.H, self.d, self.rank).transpose(1, 2).contiguous()
@@ -94,13 +115,14 @@ class LatentAttention(Mixer):
         self._no_rope = torch.zeros(0, dtype=torch.float32, device=self.env.device)
 
     def weight_bytes(self):
-        return sum(w.numel() * w.element_size() for w in (self.w_in, self.w_ukT, self.w_uv, self.w_o))
+        return sum(w.numel() * w.element_size() for w in (self.w_in, self.w_uq, self.w_ukT, self.w_uv, self.w_o)
+                   if w is not None)
 
     def flops(self, tokens, keys=0.0):
         if self.window:
             keys = min(keys, float(self.window))
         proj = 2.0 * tokens * (self.w_in.shape[0] * self.hidden + self.H * self.dv * self.hidden
-                               + self.H * self.rank * (self.d + self.dv))
+                               + self.H * self.rank * (self.d + self.dv) + self.q_rank * self.H * (self.d + self.rot))
         return proj + 2.0 * tokens * keys * self.H * (2 * self.rank + self.rot)
 
     def cache_request(self):
@@ -114,15 +136,27 @@ class LatentAttention(Mixer):
         rot = self.rope.rotation() if self.rope is not None else None
         inv_freq = rot[0] if rot is not None else self._no_rope
         proj = ops.linear(h, self.w_in, torch.float32, ctx.err)
-        q_plain, q_full = ops.latent_prepare(proj, self.H, self.d, self.rot, self.rank, self.c_weight, self.eps,
+        kv, first = None, self.H * (self.d + self.rot)
+        if self.q_rank:
+            # the queries' latent, normed in float32, then the queries: a second product, its output is what the
+            # prepare kernel reads the queries from; the latent and the key part stay in the first product's
+            cq = ops.slice_rmsnorm(proj[:, :self.q_rank], self.cq_weight, self.eps, self.env.dtype)
+            kv, first = proj[:, self.q_rank:], self.q_rank
+            q_src = ops.linear(cq, self.w_uq, torch.float32, ctx.err)
+        else:
+            q_src = proj
+        q_plain, q_full = ops.latent_prepare(q_src, self.H, self.d, self.rot, self.rank, self.c_weight, self.eps,
                                              inv_freq, cache.k_pages, ctx, cache.block_table, self.env.dtype,
-                                             write=cache.writes and not self.shares_cache)
+                                             write=cache.writes and not self.shares_cache, kv=kv, halves=self.halves)
         ops.head_linear(q_plain, self.w_ukT, q_full)
         mixed = ops.latent_attention(q_full, cache.k_pages, ctx, cache.block_table, self.rank, self.scale,
                                      self.window, self.env.dtype, ctx.plan(LATENT_WORK))
         a = torch.empty((T, self.H, self.dv), dtype=self.env.dtype, device=h.device)
         ops.head_linear(mixed, self.w_uv, a)
         a = a.view(T, self.H * self.dv)
+        if self.head_gate:
+            g0 = first + self.rank + self.rot
+            ops.sigmoid_gate_mul_(a, proj[:, g0:g0 + self.H], self.dv)
         if add_to is not None and ops.linear_add(add_to, a, self.w_o):
             return None
         return ops.linear_parts(a, self.w_o, ctx.err)

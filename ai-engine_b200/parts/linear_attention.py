@@ -105,3 +105,59 @@ class DecayLinearAttention(Mixer):
         if add_to is not None and ops.linear_add(add_to, y, self.w_o):
             return None
         return ops.linear_parts(y, self.w_o, ctx.err)
+
+
+class ForgetGateLinearAttention(Mixer):
+    """Linear attention without keys, in which the forget gate also decides what is written (HGRN2):
+
+        q = silu(W_q h),  v = W_v h,  f = l + (1 - l) sigmoid(W_f h + b_f)          (l: a lower bound per channel)
+        S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T,    o_t = S_t^T q_t                (S: [key_dim, value_dim], float32)
+
+    Each head's output is divided by its root mean square over value_dim, times a weight shared by the heads, and
+    projected by W_o.  The gate, its complement and the query's activation are made in float32 from the projection's
+    float32 output inside the recurrence kernel, as the tokens' rows are staged.
+
+    params: hidden_size, num_heads, key_dim, value_dim, eps.  tensors: q, f [H d, hidden], f_bias, lower [H d],
+    v [H dv, hidden], norm [dv], o [hidden, H dv]."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        p = spec.params
+        self.hidden, self.H = int(p["hidden_size"]), int(p["num_heads"])
+        self.d, self.dv, self.eps = int(p["key_dim"]), int(p["value_dim"]), float(p["eps"])
+        self.w_in = self.w_o = self.f_bias = self.lower = self.out_weight = None
+
+    def tensor_specs(self):
+        t, Hd, Hv = self.spec.tensors, self.H * self.d, self.H * self.dv
+        return [TensorSpec(t["q"], (Hd, self.hidden)), TensorSpec(t["f"], (Hd, self.hidden)),
+                TensorSpec(t["f_bias"], (Hd,), mean=1.0, std=1.0), TensorSpec(t["lower"], (Hd,), mean=0.3, std=0.1),
+                TensorSpec(t["v"], (Hv, self.hidden)), TensorSpec(t["norm"], (self.dv,), init="ones"),
+                TensorSpec(t["o"], (self.hidden, Hv))]
+
+    def load(self, source):
+        t = self.spec.tensors
+        ws = [source.get(t[n]) for n in ("q", "f", "v")]
+        dt = torch.float32 if any(w.dtype == torch.float32 for w in ws) else ws[0].dtype
+        self.w_in = torch.cat([w.to(dt) for w in ws], dim=0).contiguous()          # [q | f | v]
+        self.f_bias = source.get(t["f_bias"]).float().contiguous()
+        self.lower = source.get(t["lower"]).float().contiguous()
+        self.out_weight = source.get(t["norm"]).float().contiguous()
+        self.w_o = source.get(t["o"])
+
+    def weight_bytes(self):
+        return sum(w.numel() * w.element_size() for w in (self.w_in, self.w_o))
+
+    def flops(self, tokens, keys=0.0):
+        return 2.0 * tokens * self.hidden * (self.w_in.shape[0] + self.H * self.dv) + 4.0 * tokens * self.H * self.d * self.dv
+
+    def state_request(self):
+        return StateRequest((self.H, self.d, self.dv), torch.float32)
+
+    def forward(self, h, ctx, cache, add_to=None):
+        Hd = self.H * self.d
+        proj = ops.linear(h, self.w_in, torch.float32, ctx.err)
+        q, z, v = proj[:, :Hd], proj[:, Hd:2 * Hd], proj[:, 2 * Hd:]
+        o = ops.linear_recurrence(q, None, v, z, None, 1.0, 1.0, cache.state, ctx, self.H, self.d, self.dv,
+                                  forget_lower=self.lower, forget_bias=self.f_bias)
+        y = ops.head_norm_gate(o, None, self.out_weight, self.eps, self.env.dtype)
+        return ops.linear_parts(y, self.w_o, ctx.err)

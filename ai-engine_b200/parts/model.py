@@ -64,6 +64,14 @@ class Model:
                                                   self.order[rs.cache_from].cache_from is None):
                 raise ValueError(f"run order entry {i}: cache_from must name an earlier entry "
                                  f"that has a cache of its own")
+        # a block that can make the next block's input norm on its way out is told which norm that is; only when
+        # every layer runs once is "the next block" the same at every run
+        runs = [rs.layer for rs in self.order]
+        if len(set(runs)) == len(runs):
+            for a, b in zip(runs, runs[1:]):
+                blk, nxt = self.layers[a].block, self.layers[b].block
+                if hasattr(blk, "set_next_norm") and hasattr(nxt, "first_norm"):
+                    blk.set_next_norm(nxt.first_norm())
         self.keeps_embedding_output = any(getattr(l.block, "needs_embedding_output", False) for l in self.layers)
         self.loaded = False
 
@@ -153,6 +161,7 @@ class Model:
     def forward(self, ctx, cache, streams: Optional[list] = None) -> torch.Tensor:
         """`streams`: a list that receives the residual stream [T, hidden] (float32, a copy) behind every entry
         of the run order, for looking at a model layer by layer."""
+        ctx.normed_ahead = None           # (norm, its output): made ahead by the block before the one that owns the norm
         x = self.embedding.forward(ctx)
         for pe in self.env.position_encodings.values():
             pe.add_to(x, ctx)

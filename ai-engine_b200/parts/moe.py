@@ -102,9 +102,16 @@ class RoutedMoE(FeedForward):
 
     The router's last `identity` outputs have no tensors: such an expert's output is h itself.
 
+    Variants, each a parameter: `score` "sigmoid": s_e = sigmoid(z_e), every output on its own; `group_top` n: a group
+    counts as the sum of its n largest choice values; `normalise`: the chosen weights are divided by their sum
+    (+ 1e-20); `route_scale` multiplies them; no tensor `correction`: the choice is made on s itself; a shared
+    expert of the same form (`shared_intermediate_size`) runs for every token and is added.
+
     params: hidden_size, num_experts (with tensors), identity (default 0), top, intermediate_size, groups
-    (default 1), keep (default 1), activation (default "silu").  tensors: router [num_experts + identity, hidden],
-    correction [num_experts + identity]; gate, up, down as patterns with `{e}` for the expert's index."""
+    (default 1), keep (default 1), activation (default "silu"), score (default "softmax"), group_top (default 1),
+    normalise (default False), route_scale (default 1), shared_intermediate_size (default 0).  tensors: router
+    [num_experts + identity, hidden], correction [num_experts + identity] (optional); gate, up, down as patterns with
+    `{e}` for the expert's index; shared_gate, shared_up, shared_down."""
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -119,15 +126,35 @@ class RoutedMoE(FeedForward):
         if total % self.groups or not 1 <= self.keep <= self.groups or not 1 <= self.top <= total // self.groups * self.keep:
             raise ValueError(f"routed experts: {total} router outputs do not divide into {self.groups} groups of which "
                              f"{self.keep} are kept for {self.top} choices")
+        self.score = p.get("score") or "softmax"
+        if self.score not in ("softmax", "sigmoid"):
+            raise ValueError(f"routed experts: score `{self.score}` is not known (softmax, sigmoid)")
+        self.group_top, self.normalise = int(p.get("group_top") or 1), bool(p.get("normalise"))
+        self.route_scale = float(p.get("route_scale") if p.get("route_scale") is not None else 1.0)
+        self.has_correction = "correction" in spec.tensors
+        self.Fs = int(p.get("shared_intermediate_size") or 0)
+        self.shared = None
+        if self.Fs:
+            from .registry import lookup
+            from .spec import PartSpec
+            t = spec.tensors
+            self.shared = lookup("feed_forward", "swiglu")(PartSpec("swiglu", dict(
+                hidden_size=self.hidden, intermediate_size=self.Fs, activation=self.activation),
+                dict(gate=t["shared_gate"], up=t["shared_up"], down=t["shared_down"])), env)
         self.w_router = self.correction = self.w_gu = self.w_down = None
+
+    def sub_parts(self):
+        return {"shared": self.shared} if self.shared is not None else {}
 
     def tensor_specs(self):
         t, D, total = self.spec.tensors, self.hidden, self.E + self.ident
-        specs = [TensorSpec(t["router"], (total, D), std=0.3), TensorSpec(t["correction"], (total,), std=0.05)]
+        specs = [TensorSpec(t["router"], (total, D), std=0.3)]
+        if self.has_correction:
+            specs.append(TensorSpec(t["correction"], (total,), std=0.05))
         for e in range(self.E):
             specs += [TensorSpec(t["gate"].format(e=e), (self.F, D)), TensorSpec(t["up"].format(e=e), (self.F, D)),
                       TensorSpec(t["down"].format(e=e), (D, self.F))]
-        return specs
+        return specs + (self.shared.tensor_specs() if self.shared is not None else [])
 
     def load(self, source):
         t = self.spec.tensors
@@ -136,7 +163,10 @@ class RoutedMoE(FeedForward):
             # zero rows up to a multiple of 8: the tensor-core products want rows of the output 16 bytes apart
             pad = torch.zeros(((-self.w_router.shape[0]) % 8, self.hidden), dtype=torch.bfloat16, device=self.w_router.device)
             self.w_router = torch.cat([self.w_router, pad], dim=0).contiguous()
-        self.correction = source.get(t["correction"]).float().contiguous()
+        if self.has_correction:
+            self.correction = source.get(t["correction"]).float().contiguous()
+        if self.shared is not None:
+            self.shared.load(source)
         gu, down = [], []
         for e in range(self.E):
             gu += [source.get(t["gate"].format(e=e)), source.get(t["up"].format(e=e))]
@@ -148,10 +178,12 @@ class RoutedMoE(FeedForward):
 
     def weight_bytes(self):
         """What a step of many tokens reads: every expert once."""
-        return sum(w.numel() * w.element_size() for w in (self.w_router, self.w_gu, self.w_down) if w is not None)
+        return sum(w.numel() * w.element_size() for w in (self.w_router, self.w_gu, self.w_down) if w is not None) \
+            + (self.shared.weight_bytes() if self.shared is not None else 0)
 
     def flops(self, tokens, keys=0.0):
-        return 2.0 * tokens * self.hidden * (3 * self.top * self.F + self.E + self.ident)
+        return 2.0 * tokens * self.hidden * (3 * self.top * self.F + self.E + self.ident) \
+            + (self.shared.flops(tokens, keys) if self.shared is not None else 0.0)
 
     def forward(self, h, ctx):
         # the router in float32 on the sublayer's input as the experts see it: products of bfloat16 values are exact
@@ -160,13 +192,15 @@ class RoutedMoE(FeedForward):
             logits = ops.linear(h, self.w_router, torch.float32, ctx.err)[:, :self.E + self.ident]
         else:
             logits = ops.gemm_f32(ops.cast(h, torch.float32), self.w_router)
-        ids, weights = ops.route_topk(logits, self.correction, self.groups, self.keep, self.top)
+        ids, weights = ops.route_topk(logits, self.correction, self.groups, self.keep, self.top, score=self.score,
+                                      group_top=self.group_top, normalise=self.normalise, weight_scale=self.route_scale)
+        shared = self.shared.forward(h, ctx) if self.shared is not None else None
         if not self.E:
             y = torch.zeros((1, self.hidden), dtype=torch.float32, device=h.device)
             pair_row = torch.full((ids.numel(),), -2, dtype=torch.int32, device=h.device)
-            return ops.expert_combine_weighted(y, pair_row, weights, h)
+            return ops.expert_combine_weighted(y, pair_row, weights, h, shared)
         row_token, pair_row, tile_expert = ops.expert_plan(None, ids, self.E, ctx.err, identity=self.ident)
         gu = ops.grouped_linear(h, self.w_gu, tile_expert, torch.float32, ctx.err, row_src=row_token)
         act = ops.clamped_glu(gu, self.F, float("inf"), 1.0, 0.0, self.env.dtype)       # silu(gate) * up
         y = ops.grouped_linear(act, self.w_down, tile_expert, torch.float32, ctx.err)
-        return ops.expert_combine_weighted(y, pair_row, weights, h)
+        return ops.expert_combine_weighted(y, pair_row, weights, h, shared)

@@ -37,3 +37,36 @@ class RMSNorm(Norm):
     def forward(self, x, delta=None, rows=None, write_back=True):
         return ops.add_rmsnorm(x, delta, self.weight, self.eps, self.out_dtype, rows=rows,
                                write_back=write_back)
+
+
+class DynamicTanh(Norm):
+    """A norm that computes no mean and no variance: y = tanh(alpha x) * w + b, element by element in float32.
+    params: size; output (default "compute", or "float32").  tensors: weight [size], bias [size], alpha (one number).
+    The add of a pending branch is fused in.  `ahead()` hands (weight, bias, alpha) to a kernel that already holds
+    the stream's new value and can make this norm's output on the way."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.size = int(spec.params["size"])
+        self.out_dtype = torch.float32 if spec.params.get("output") == "float32" else env.dtype
+        self.weight = self.bias = self.alpha = None
+
+    def tensor_specs(self):
+        t = self.spec.tensors
+        return [TensorSpec(t["weight"], (self.size,), init="ones"), TensorSpec(t["bias"], (self.size,), init="zeros"),
+                TensorSpec(t["alpha"], (), mean=0.5, std=0.05)]
+
+    def load(self, source):
+        t = self.spec.tensors
+        self.weight = source.get(t["weight"]).float().contiguous()
+        self.bias = source.get(t["bias"]).float().contiguous()
+        self.alpha = source.get(t["alpha"]).float().reshape(1).contiguous()
+
+    def weight_bytes(self):
+        return 2 * self.size * 4
+
+    def ahead(self):
+        return self.weight, self.bias, self.alpha
+
+    def forward(self, x, delta=None, rows=None, write_back=True):
+        return ops.add_dyt(x, delta, self.weight, self.bias, self.alpha, self.out_dtype, rows=rows, write_back=write_back)
