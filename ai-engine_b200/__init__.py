@@ -3,10 +3,10 @@ B200 (sm_100a): typed configuration and registry, safetensors weights, layers
 from parts, a paged cache, one step function, a scheduler, sampling, and trace
 replay, on hand-written CUDA kernels."""
 from . import models  # noqa: F401  (registers the architectures)
-from .config import ConfigError, LlamaConfig, PifutarConfig, TizodraConfig, ZupitarConfig, load_config, register_architecture
+from .config import ConfigError, FokisunConfig, LlamaConfig, PifutarConfig, TizodraConfig, ZupitarConfig, load_config, register_architecture
 from .weights import WeightError, write_random_model
 
-__all__ = ["ConfigError", "LlamaConfig", "PifutarConfig", "ZupitarConfig", "TizodraConfig", "load_config", "register_architecture", "WeightError",
+__all__ = ["ConfigError", "LlamaConfig", "PifutarConfig", "ZupitarConfig", "TizodraConfig", "FokisunConfig", "load_config", "register_architecture", "WeightError",
            "write_random_model", "Engine", "SamplingParams", "EngineOptions"]
 
 

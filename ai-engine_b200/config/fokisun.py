@@ -193,10 +193,10 @@ class FokisunConfig:
             m = _obj(l, "mixer", where)
             mixer = _named(lambda: FokisunMixer.from_dict(kind, m, where + "mixer."), where + "mixer.")
             if mixer.v_mix:
-                if mixed is not None and (mixer.kv_heads * mixer.vdim) != mixed:
-                    raise ConfigError(f"config.json: {where}mixer: layers that mix values need kv_heads * vdim = {mixed} "
-                                      f"like the first of them")
-                mixed = mixer.kv_heads * mixer.vdim
+                if mixed is not None and (mixer.kv_heads, mixer.vdim) != mixed:
+                    raise ConfigError(f"config.json: {where}mixer: layers that mix values need kv_heads = {mixed[0]} and "
+                                      f"vdim = {mixed[1]} like the first of them")
+                mixed = (mixer.kv_heads, mixer.vdim)
             f = _obj(l, "mlp", where, required=False)
             layers.append(FokisunLayer(kind, mixer, FokisunFF.from_dict(f, where + "mlp.") if f else None))
         eos = raw.get("eos_token_id")

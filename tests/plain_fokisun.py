@@ -104,7 +104,7 @@ def attention(h, W, p, m, eps, v_first):
     values mixed with the first such layer's, a gate element by element.  Returns (output, this layer's values as
     they are cached)."""
     T = h.shape[0]
-    H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, G, d, dv = m["heads"], m.get("kv_heads", m["heads"]), m["dim"], m["vdim"]
     pos = torch.arange(T)
     q = rms(h @ W[p + "q"].T + W[p + "q.b"], W[p + "q.norm"], eps).view(T, H, d)
     k = rms(h @ W[p + "k"].T + W[p + "k.b"], W[p + "k.norm"], eps).view(T, G, d)
@@ -136,8 +136,10 @@ def gated_ff(h, W, p, act):
     return (act(h @ W[p + "gate"].T) * (h @ W[p + "up"].T)) @ W[p + "down"].T
 
 
-def route(h, W, p, router):
-    """(chosen experts [T, top], their weights [T, top])."""
+def route(h, W, p, router, margins_out=None):
+    """(chosen experts [T, top], their weights [T, top]).  margins_out: a list that receives, per token, how far
+    the choice is from turning (the last open group's lead over the first closed one, the last chosen score's over
+    the first one left out; the smaller of the two)."""
     E, top = router["experts"], router["top"]
     groups = router.get("groups") or {"count": 1, "keep": 1}
     s = torch.sigmoid(h @ W[p + "router"].T)
@@ -148,11 +150,18 @@ def route(h, W, p, router):
     masked = s.masked_fill(~open_.repeat_interleave(per, dim=1), float("-inf"))
     ids = masked.topk(top, dim=-1).indices
     w = s.gather(1, ids)
+    if margins_out is not None:
+        inf = torch.full((s.shape[0],), float("inf"), dtype=s.dtype)
+        gsort = gs.sort(dim=-1, descending=True).values
+        gm = gsort[:, groups["keep"] - 1] - gsort[:, groups["keep"]] if groups["keep"] < groups["count"] else inf
+        msort = masked.sort(dim=-1, descending=True).values
+        em = msort[:, top - 1] - msort[:, top] if top < per * groups["keep"] else inf
+        margins_out.append(torch.minimum(gm, em))
     return ids, w / (w.sum(dim=-1, keepdim=True) + 1e-20) * router["scale"]
 
 
-def moe_ff(h, W, p, f):
-    ids, w = route(h, W, p, f["router"])
+def moe_ff(h, W, p, f, margins_out=None):
+    ids, w = route(h, W, p, f["router"], margins_out)
     out = torch.zeros(h.shape[0], W[p + "e0.down"].shape[0], dtype=h.dtype)
     for t in range(h.shape[0]):
         for e, we in zip(ids[t].tolist(), w[t]):
@@ -162,10 +171,11 @@ def moe_ff(h, W, p, f):
     return out
 
 
-def forward(cfg, weights, tokens, dtype=torch.float64):
-    """(logits [T, vocab], the stream behind every layer [L, T, width])."""
+def forward(cfg, weights, tokens, dtype=torch.float64, margins_out=None):
+    """(logits [T, vocab], the stream behind every layer [L, T, width]).  margins_out: see `route`, one entry a
+    routed layer."""
     W = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in weights.items()}
-    eps, m_res = cfg["norm"]["eps"], cfg["residual_mult"]
+    eps, m_res = cfg["norm"]["eps"], cfg.get("residual_mult", 1.0)
     x = W["embed"][torch.as_tensor(tokens, dtype=torch.long)]
     history, streams = [x], []
     v_first = None
@@ -184,10 +194,10 @@ def forward(cfg, weights, tokens, dtype=torch.float64):
             raise ValueError(l["type"])
         f = l.get("mlp")
         if f:
-            a = a + (gated_ff(h, W, p + "mlp.", gelu_tanh) if f["kind"] == "dense" else moe_ff(h, W, p + "mlp.", f))
+            a = a + (gated_ff(h, W, p + "mlp.", gelu_tanh) if f["kind"] == "dense" else moe_ff(h, W, p + "mlp.", f, margins_out))
         history.append(x + m_res * a)
         coef = W[p + "dwa"]
         x = sum(coef[j] * history[j] for j in range(i + 2))
         streams.append(x)
     h = dyt(x, W["final.norm"], W["final.norm.b"], W["final.norm.alpha"])
-    return (h @ W["embed"].T) * cfg["logit_scale"], torch.stack(streams)
+    return (h @ W["embed"].T) * cfg.get("logit_scale", 1.0), torch.stack(streams)
