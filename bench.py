@@ -110,6 +110,28 @@ def tizodra_shape(width, layers=8):
                 loop=dict(start=0, stop=3, times=2), layers=out)
 
 
+def fokisun_shape(width, layers=8):
+    """A Fokisun configuration with layers of the sizes real models of its kind have: attention heads of 128 for keys and
+    values (a quarter of them key/value heads, the whole head rotated, positions stretched by 4) under a window of 1,024
+    keys, values mixed from the first attention layer on; HGRN2 heads of 128 x 128; latent-attention heads of 128 + 64
+    rotated with a latent of width / 4 (256 to 512) and a query latent of 3 / 8 width; a dense first layer of 3 x width,
+    then experts of width / 2 (top 4 of 32, two of four groups kept) beside a shared one of `width`.  The pattern
+    (hgrn2, attention, latent attention) repeats."""
+    H = width // 128
+    att = dict(type="attention", mixer=dict(heads=H, kv_heads=max(1, H // 4), dim=128, vdim=128, scale=128 ** -0.5,
+                                            mask=dict(size=1024), v_mix=True,
+                                            rot=dict(base=500000.0, dims=128, scaling=dict(factor=4.0))))
+    rec = dict(type="hgrn2", mixer=dict(heads=H, dim=128, vdim=128))
+    lat = dict(type="latent_attention", mixer=dict(heads=H, dim=128, rot_dim=64, vdim=128, kv_rank=min(512, max(256, width // 4)),
+                                                   q_rank=max(384, 3 * width // 8), scale=192 ** -0.5,
+                                                   rot=dict(base=500000.0, dims=64)))
+    moe = dict(kind="moe", expert=dict(ff=width // 2), shared=dict(ff=width),
+               router=dict(experts=32, top=4, scale=2.5, groups=dict(count=4, keep=2)))
+    out = [dict((rec, att, lat)[i % 3], mlp=dict(kind="dense", ff=3 * width) if i == 0 else moe) for i in range(layers)]
+    return dict(architecture="Fokisun", vocab=32000, width=width, norm=dict(eps=1e-5), residual_mult=0.7, logit_scale=1.0,
+                layers=out)
+
+
 def llama_like(width, layers=8):
     """The closest existing model at equal size: the same width, layers, heads of 128 (a quarter of them kv heads)
     and a feed-forward of 3 x width, which is what a Pifutar token uses (4 experts of width / 2 + the shared one)."""
@@ -652,10 +674,10 @@ def main():
                     help="time one part only and print its numbers (for profiling)")
     ap.add_argument("--profile", action="store_true",
                     help="CUDA-event time, bytes, flops and roofline fraction per class of kernel (eager launches)")
-    ap.add_argument("--shape", choices=["8b", "1b", "3b"] + [f"{m}-{w}" for m in ("pifutar", "zupitar", "tizodra", "llama") for w in WIDTHS],
+    ap.add_argument("--shape", choices=["8b", "1b", "3b"] + [f"{m}-{w}" for m in ("pifutar", "zupitar", "tizodra", "fokisun", "llama") for w in WIDTHS],
                     default="8b",
                     help="layer sizes for --profile and --only decode|prefill (the headline run is always the 8B shape); "
-                         "pifutar-1k|2k|4k, zupitar-1k|2k|4k, tizodra-1k|2k|4k: those designs at that width, llama-1k|2k|4k: Llama at equal size beside them "
+                         "pifutar-1k|2k|4k, zupitar-1k|2k|4k, tizodra-1k|2k|4k, fokisun-1k|2k|4k: those designs at that width, llama-1k|2k|4k: Llama at equal size beside them "
                          "(8 layers unless --layers says otherwise)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="cached tokens per request for --profile / --only decode")
     ap.add_argument("--skip-workloads", action="store_true", help="leave the 1B and 3B serving workloads out of `points`")
@@ -702,7 +724,7 @@ def main():
     if "-" in a.shape and (a.profile or a.only):
         family, w = a.shape.split("-")
         layers = a.layers if a.layers != LLAMA3_8B["num_hidden_layers"] else 8
-        cfg = dict(pifutar=pifutar_shape, zupitar=zupitar_shape, tizodra=tizodra_shape, llama=llama_like)[family](WIDTHS[w], layers)
+        cfg = dict(pifutar=pifutar_shape, zupitar=zupitar_shape, tizodra=tizodra_shape, fokisun=fokisun_shape, llama=llama_like)[family](WIDTHS[w], layers)
     else:
         cfg = dict({"8b": LLAMA3_8B, "1b": LLAMA32_1B, "3b": LLAMA32_3B}.get(a.shape, LLAMA3_8B) if (a.profile or a.only) else LLAMA3_8B)
         if a.layers != LLAMA3_8B["num_hidden_layers"] or a.shape == "8b":
