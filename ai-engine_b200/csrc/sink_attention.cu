@@ -79,20 +79,18 @@ extern "C" int aie_sink_attn_prepare(const float* proj, int ld, const float* bia
     AIE_LAUNCH_CHECK();
 }
 
-// x [n] holds whole heads of `d` elements; element c after the rotation by `pos` of its head's first rot_dims elements
-__device__ __forceinline__ float head_rotated(const float* x, int c, int d, int rot_dims, int halves, int pos,
-                                              const float* __restrict__ inv_freq) {
-    const int i = c % d;
-    if (i >= rot_dims) return x[c];
-    const int half = rot_dims >> 1;
+// The two elements of pair j (of rot_dims / 2) of a head that starts at x, turned by `pos`: neighbours (2j, 2j + 1) or,
+// with `halves`, (j, j + rot_dims / 2).  One sincosf a pair.
+__device__ __forceinline__ void head_pair_rotated(const float* x, int j, int rot_dims, int halves, int pos,
+                                                  const float* __restrict__ inv_freq, int* ia, int* ib, float* ya,
+                                                  float* yb) {
+    const int a = halves ? j : 2 * j, b = halves ? j + (rot_dims >> 1) : 2 * j + 1;
     float sn, cs;
-    if (halves) {
-        const int j = i < half ? i : i - half;
-        sincosf((float)pos * inv_freq[j], &sn, &cs);
-        return i < half ? x[c] * cs - x[c + half] * sn : x[c] * cs + x[c - half] * sn;
-    }
-    sincosf((float)pos * inv_freq[i >> 1], &sn, &cs);
-    return (i & 1) ? x[c] * cs + x[c - 1] * sn : x[c] * cs - x[c + 1] * sn;
+    sincosf((float)pos * inv_freq[j], &sn, &cs);
+    *ia = a;
+    *ib = b;
+    *ya = x[a] * cs - x[b] * sn;
+    *yb = x[b] * cs + x[a] * sn;
 }
 
 // proj [T, >= H d + G d + G e] float32; bias [H d + G d + G e] or null; q_w [H d], k_w [G d] float32 or null (no norm).
@@ -135,20 +133,39 @@ normed_attn_prepare_kernel(const float* __restrict__ proj, int ld, const float* 
     }
     __syncthreads();
     const int pos = positions[t];
-    for (int c = tid; c < nq; c += blockDim.x)
-        q_out[(size_t)t * nq + c] = from_f32<A>(rot_dims > 0 ? head_rotated(qs, c, d, rot_dims, halves, pos, inv_freq) : qs[c]);
+    const int half = rot_dims >> 1, rest = d - rot_dims;
+    for (int p = tid; p < H * half; p += blockDim.x) {            // a thread a pair
+        const int hh = p / half, j = p - hh * half;
+        int ia, ib;
+        float ya, yb;
+        head_pair_rotated(qs + hh * d, j, rot_dims, halves, pos, inv_freq, &ia, &ib, &ya, &yb);
+        q_out[(size_t)t * nq + hh * d + ia] = from_f32<A>(ya);
+        q_out[(size_t)t * nq + hh * d + ib] = from_f32<A>(yb);
+    }
+    for (int p = tid; p < H * rest; p += blockDim.x) {            // what the rotation leaves as it is
+        const int c = (p / rest) * d + rot_dims + p % rest;
+        q_out[(size_t)t * nq + c] = from_f32<A>(qs[c]);
+    }
     const int pidx = pos / P;
     const int page = (pos >= 0 && pidx < bt_width) ? block_table[(size_t)token_req[t] * bt_width + pidx] : -1;
     const bool page_ok = page >= 0 && page < num_pages;
     if (write && !page_ok && tid == 0) atomicOr(err, AIE_DEV_PAGE_OOB);
     const int w = d + e;
     A* base = pages + ((size_t)(page_ok ? page : 0) * G * P + (pos % P)) * w;
-    if (write && page_ok)
-        for (int c = tid; c < nk; c += blockDim.x) {
-            const int g = c / d;
-            base[(size_t)g * P * w + (c - g * d)] =
-                from_f32<A>(rot_dims > 0 ? head_rotated(ks, c, d, rot_dims, halves, pos, inv_freq) : ks[c]);
+    if (write && page_ok) {
+        for (int p = tid; p < G * half; p += blockDim.x) {
+            const int g = p / half, j = p - g * half;
+            int ia, ib;
+            float ya, yb;
+            head_pair_rotated(ks + g * d, j, rot_dims, halves, pos, inv_freq, &ia, &ib, &ya, &yb);
+            base[(size_t)g * P * w + ia] = from_f32<A>(ya);
+            base[(size_t)g * P * w + ib] = from_f32<A>(yb);
         }
+        for (int p = tid; p < G * rest; p += blockDim.x) {
+            const int g = p / rest, i = rot_dims + p % rest;
+            base[(size_t)g * P * w + i] = from_f32<A>(ks[g * d + i]);
+        }
+    }
     const float lam = mix_from ? lambda[0] : 0.f;
     for (int c = tid; c < nv; c += blockDim.x) {
         float v = row[nq + nk + c] + (bias ? bias[nq + nk + c] : 0.f);
