@@ -112,7 +112,7 @@ def tizodra_shape(width, layers=8):
 
 def fokisun_shape(width, layers=8):
     """A Fokisun configuration with layers of the sizes real models of its kind have: attention heads of 128 for keys and
-    values (a quarter of them key/value heads, the whole head rotated, positions stretched by 4) under a window of 1,024
+    values (a quarter of them key/value heads, the whole head rotated, positions stretched by 8) under a window of 1,024
     keys, values mixed from the first attention layer on; HGRN2 heads of 128 x 128; latent-attention heads of 128 + 64
     rotated with a latent of width / 4 (256 to 512) and a query latent of 3 / 8 width; a dense first layer of 3 x width,
     then experts of width / 2 (top 4 of 32, two of four groups kept) beside a shared one of `width`.  The pattern
@@ -120,15 +120,15 @@ def fokisun_shape(width, layers=8):
     H = width // 128
     att = dict(type="attention", mixer=dict(heads=H, kv_heads=max(1, H // 4), dim=128, vdim=128, scale=128 ** -0.5,
                                             mask=dict(size=1024), v_mix=True,
-                                            rot=dict(base=500000.0, dims=128, scaling=dict(factor=4.0))))
+                                            rot=dict(base=500000.0, dims=128, scaling=dict(factor=8.0))))
     rec = dict(type="hgrn2", mixer=dict(heads=H, dim=128, vdim=128))
     lat = dict(type="latent_attention", mixer=dict(heads=H, dim=128, rot_dim=64, vdim=128, kv_rank=min(512, max(256, width // 4)),
                                                    q_rank=max(384, 3 * width // 8), scale=192 ** -0.5,
                                                    rot=dict(base=500000.0, dims=64)))
     moe = dict(kind="moe", expert=dict(ff=width // 2), shared=dict(ff=width),
-               router=dict(experts=32, top=4, scale=2.5, groups=dict(count=4, keep=2)))
+               router=dict(experts=32, top=4, scale=2.0, groups=dict(count=4, keep=2)))
     out = [dict((rec, att, lat)[i % 3], mlp=dict(kind="dense", ff=3 * width) if i == 0 else moe) for i in range(layers)]
-    return dict(architecture="Fokisun", vocab=32000, width=width, norm=dict(eps=1e-5), residual_mult=0.7, logit_scale=1.0,
+    return dict(architecture="Fokisun", vocab=32000, width=width, norm=dict(eps=1e-5), residual_mult=0.8, logit_scale=1.0,
                 layers=out)
 
 

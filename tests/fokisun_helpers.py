@@ -67,9 +67,9 @@ CFG_A = dict(architecture="Fokisun", vocab=211, width=96, norm=dict(eps=1e-4), r
 # the sizes the tensor-core kernels take in bfloat16 (keys and values of 64 and 128, a value of 32; a latent of 64 and
 # of 128; experts whose width is a multiple of 64), a window that a 128-token tile crosses, an attention without a window
 CFG_B = dict(architecture="Fokisun", vocab=257, width=128, norm=dict(eps=1e-5), residual_mult=0.8, logit_scale=3.0, layers=[
-    layer(attn(4, 2, 64, 64, 0.125, 70, (250000.0, 64, 4.0), v_mix=True), moe(64, 4, 2, 2, 1, 2.5, shared=64)),
+    layer(attn(4, 2, 64, 64, 0.13, 70, (40000.0, 64, 3.0), v_mix=True), moe(64, 4, 2, 2, 1, 1.5, shared=64)),
     layer(hgrn(2, 64, 64), dense(256)),
-    layer(latent(4, 32, 16, 32, 64, 96, 0.14)),
+    layer(latent(4, 32, 16, 48, 64, 96, 0.15)),
     layer(attn(2, 2, 128, 64, 0.09, None, (10000.0, 32, None), v_mix=True), dense(192)),
     layer(latent(2, 64, 32, 64, 128, 64, 0.1, 50000.0), moe(128, 2, 1)),
     layer(attn(4, 1, 64, 32, 0.2, 130, (10000.0, 64, None)), dense(128)),

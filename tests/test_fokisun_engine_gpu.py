@@ -247,7 +247,7 @@ def drawn_config(seed):
             per = r.choice([1, 2, 3])
             keep = r.randint(1, count)
             mlp = moe(r.choice([16, 24, 64, 96]), count * per, r.randint(1, per * keep), count, keep,
-                      r.choice([0.5, 1.0, 2.5]), r.choice([None, 16, 64]))
+                      r.choice([0.5, 1.0, 2.0]), r.choice([None, 16, 64]))
         if kind == "attention":
             v_mix = r.random() < 0.6
             kv, vdim = mix_shape if v_mix else (r.choice([1, 2, 3, 4]), r.choice([4, 16, 32, 36, 64, 128]))
@@ -255,7 +255,7 @@ def drawn_config(seed):
             dim = r.choice([8, 12, 32, 40, 64, 96, 128])
             rot = None
             if r.random() < 0.8:
-                rot = (r.choice([100.0, 10000.0, 250000.0]), r.choice([x for x in (2, 4, 8, 12, 32, 64, 128) if x <= dim]),
+                rot = (r.choice([100.0, 10000.0, 200000.0]), r.choice([x for x in (2, 4, 8, 12, 32, 64, 128) if x <= dim]),
                        r.choice([None, 2.0, 4.0]))
             layers.append(layer(attn(heads, kv, dim, vdim, r.uniform(0.05, 0.4), r.choice([None, 1, 3, 17, 40, 64, 100]),
                                      rot, v_mix), mlp))
@@ -267,7 +267,7 @@ def drawn_config(seed):
                                        r.choice([8, 16, 32, 40]), r.choice([8, 24, 64, 128]), r.choice([8, 20, 64, 128]),
                                        r.uniform(0.05, 0.3), r.choice([100.0, 50000.0])), mlp))
     return dict(architecture="Fokisun", vocab=r.choice([61, 128, 300]), width=width,
-                norm=dict(eps=r.choice([1e-6, 1e-5, 1e-3])), residual_mult=r.choice([0.5, 0.7, 1.0, 1.4]),
+                norm=dict(eps=r.choice([1e-6, 1e-5, 1e-3])), residual_mult=r.choice([0.5, 0.75, 1.0, 1.4]),
                 logit_scale=r.choice([0.25, 1.0, 2.5]), layers=layers)
 
 
