@@ -573,6 +573,28 @@ __global__ void add_dyt_kernel(float* __restrict__ x, const A* __restrict__ delt
     }
 }
 
+// four neighbouring elements a thread: D a multiple of 4, no row pick, 16-byte aligned pointers and part strides
+template <typename A, typename O>
+__global__ void add_dyt_vec4_kernel(float* __restrict__ x, const A* __restrict__ delta, int parts, size_t part_stride,
+                                    const float* __restrict__ w, const float* __restrict__ b, const float* __restrict__ alpha,
+                                    O* __restrict__ out, int D, int write_back, size_t n) {
+    const float al = alpha[0];
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= n) return;
+    float4 s = *reinterpret_cast<const float4*>(x + i);
+    if (delta) {
+        for (int p = 0; p < parts; ++p) {
+            const float4 t = load4<A>(delta + p * part_stride + i);
+            s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+        }
+        if (write_back) *reinterpret_cast<float4*>(x + i) = s;
+    }
+    const int c = (int)(i % D);
+    const float4 wv = *reinterpret_cast<const float4*>(w + c), bv = *reinterpret_cast<const float4*>(b + c);
+    store4<O>(out + i, make_float4(fmaf(tanhf(al * s.x), wv.x, bv.x), fmaf(tanhf(al * s.y), wv.y, bv.y),
+                                   fmaf(tanhf(al * s.z), wv.z, bv.z), fmaf(tanhf(al * s.w), wv.w, bv.w)));
+}
+
 extern "C" int aie_add_dyt(float* x, const void* delta, int delta_dtype, int parts, long long part_stride, const float* w,
                            const float* b, const float* alpha, void* out, int out_dtype, const int* rows, int n_rows, int D,
                            int write_back, cudaStream_t stream) {
@@ -581,10 +603,19 @@ extern "C" int aie_add_dyt(float* x, const void* delta, int delta_dtype, int par
     const size_t n = (size_t)n_rows * D;
     int blocks = (int)((n + 255) / 256);
     if (blocks > aie_sm_count() * 16) blocks = aie_sm_count() * 16;
-#define GO(A, O)                                                                                                      \
-    add_dyt_kernel<A, O><<<blocks, 256, 0, stream>>>(x, (const A*)delta, parts, (size_t)part_stride, w, b, alpha,     \
-                                                     (O*)out, rows, D, write_back, n)
     const bool dbf = delta && delta_dtype == AIE_BF16;
+    const bool vec = !rows && D % 4 == 0 && !((size_t)x & 15) && !((size_t)w & 15) && !((size_t)b & 15) && !((size_t)out & 15) &&
+                     (!delta || (part_stride % 8 == 0 && !((size_t)delta & 15)));
+    const unsigned vblocks = (unsigned)((n / 4 + 255) / 256);
+#define GO(A, O)                                                                                                      \
+    do {                                                                                                              \
+        if (vec)                                                                                                      \
+            add_dyt_vec4_kernel<A, O><<<vblocks, 256, 0, stream>>>(x, (const A*)delta, parts, (size_t)part_stride, w, b, alpha, \
+                                                                  (O*)out, D, write_back, n);                          \
+        else                                                                                                          \
+            add_dyt_kernel<A, O><<<blocks, 256, 0, stream>>>(x, (const A*)delta, parts, (size_t)part_stride, w, b, alpha,     \
+                                                             (O*)out, rows, D, write_back, n);                        \
+    } while (0)
     if (out_dtype == AIE_F32) { if (dbf) GO(bf16, float); else GO(float, float); }
     else if (out_dtype == AIE_BF16) { if (dbf) GO(bf16, bf16); else GO(float, bf16); }
     else return AIE_BAD_ARG;
@@ -608,15 +639,44 @@ __global__ void sigmoid_gate_mul_kernel(A* __restrict__ a, const float* __restri
     }
 }
 
+// four neighbouring elements a thread: N a multiple of 4; a group is one element or a multiple of four
+template <typename A>
+__global__ void sigmoid_gate_mul_vec4_kernel(A* __restrict__ a, const float* __restrict__ g, int ldg, int N, int group, size_t n) {
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= n) return;
+    const size_t t = i / N;
+    const int c = (int)(i - t * N);
+    float4 z;
+    if (group == 1) {
+        const float* gp = g + t * ldg + c;
+        z = make_float4(gp[0], gp[1], gp[2], gp[3]);
+    } else {
+        const float zz = g[t * ldg + c / group];
+        z = make_float4(zz, zz, zz, zz);
+    }
+    float4 v = load4<A>(a + i);
+    v.x *= 1.0f / (1.0f + expf(-z.x));
+    v.y *= 1.0f / (1.0f + expf(-z.y));
+    v.z *= 1.0f / (1.0f + expf(-z.z));
+    v.w *= 1.0f / (1.0f + expf(-z.w));
+    store4<A>(a + i, v);
+}
+
 extern "C" int aie_sigmoid_gate_mul(void* a, int dtype, const float* g, int ldg, int T, int N, int group, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (N <= 0 || group <= 0 || N % group) return AIE_BAD_ARG;
     const size_t n = (size_t)T * N;
     int blocks = (int)((n + 255) / 256);
     if (blocks > aie_sm_count() * 16) blocks = aie_sm_count() * 16;
-    if (dtype == AIE_F32) sigmoid_gate_mul_kernel<float><<<blocks, 256, 0, stream>>>((float*)a, g, ldg, N, group, n);
-    else if (dtype == AIE_BF16) sigmoid_gate_mul_kernel<bf16><<<blocks, 256, 0, stream>>>((bf16*)a, g, ldg, N, group, n);
-    else return AIE_BAD_ARG;
+    const bool vec = N % 4 == 0 && (group == 1 || group % 4 == 0) && !((size_t)a & 15);
+    const unsigned vblocks = (unsigned)((n / 4 + 255) / 256);
+    if (dtype == AIE_F32) {
+        if (vec) sigmoid_gate_mul_vec4_kernel<float><<<vblocks, 256, 0, stream>>>((float*)a, g, ldg, N, group, n);
+        else sigmoid_gate_mul_kernel<float><<<blocks, 256, 0, stream>>>((float*)a, g, ldg, N, group, n);
+    } else if (dtype == AIE_BF16) {
+        if (vec) sigmoid_gate_mul_vec4_kernel<bf16><<<vblocks, 256, 0, stream>>>((bf16*)a, g, ldg, N, group, n);
+        else sigmoid_gate_mul_kernel<bf16><<<blocks, 256, 0, stream>>>((bf16*)a, g, ldg, N, group, n);
+    } else return AIE_BAD_ARG;
     AIE_LAUNCH_CHECK();
 }
 

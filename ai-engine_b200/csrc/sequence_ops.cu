@@ -191,6 +191,50 @@ extern "C" int aie_depth_average(float* x, const void* delta, int delta_dtype, i
     AIE_LAUNCH_CHECK();
 }
 
+// The same, four neighbouring elements a thread (16-byte loads and stores): n and D multiples of 4, every pointer and
+// every part's stride 16-byte aligned.
+template <typename O>
+__global__ void depth_average2_vec4_kernel(float* __restrict__ x, const float* __restrict__ a, int pa, size_t sa,
+                                           const float* __restrict__ b, int pb, size_t sb, float mult,
+                                           float* __restrict__ history, const float* __restrict__ coef, int depth, size_t n,
+                                           const float* __restrict__ norm_w, const float* __restrict__ norm_b,
+                                           const float* __restrict__ norm_alpha, O* __restrict__ normed, int D) {
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= n) return;
+    float4 d = make_float4(0.f, 0.f, 0.f, 0.f), e = d;
+    for (int p = 0; p < pa; ++p) {
+        const float4 t = *reinterpret_cast<const float4*>(a + p * sa + i);
+        d.x += t.x; d.y += t.y; d.z += t.z; d.w += t.w;
+    }
+    for (int p = 0; p < pb; ++p) {
+        const float4 t = *reinterpret_cast<const float4*>(b + p * sb + i);
+        e.x += t.x; e.y += t.y; e.z += t.z; e.w += t.w;
+    }
+    const float4 xv = *reinterpret_cast<const float4*>(x + i);
+    const float4 s = make_float4(fmaf(mult, d.x + e.x, xv.x), fmaf(mult, d.y + e.y, xv.y), fmaf(mult, d.z + e.z, xv.z),
+                                 fmaf(mult, d.w + e.w, xv.w));
+    float4 y = s;
+    if (coef) {
+        *reinterpret_cast<float4*>(history + (size_t)depth * n + i) = s;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < depth; ++j) {
+            const float c = coef[j];
+            const float4 hv = *reinterpret_cast<const float4*>(history + (size_t)j * n + i);
+            acc.x = fmaf(c, hv.x, acc.x); acc.y = fmaf(c, hv.y, acc.y); acc.z = fmaf(c, hv.z, acc.z); acc.w = fmaf(c, hv.w, acc.w);
+        }
+        const float c = coef[depth];
+        y = make_float4(fmaf(c, s.x, acc.x), fmaf(c, s.y, acc.y), fmaf(c, s.z, acc.z), fmaf(c, s.w, acc.w));
+    }
+    *reinterpret_cast<float4*>(x + i) = y;
+    if (norm_w) {
+        const int c = (int)(i % D);
+        const float al = norm_alpha[0];
+        const float4 w = *reinterpret_cast<const float4*>(norm_w + c), bb = *reinterpret_cast<const float4*>(norm_b + c);
+        store4<O>(normed + i, make_float4(fmaf(tanhf(al * y.x), w.x, bb.x), fmaf(tanhf(al * y.y), w.y, bb.y),
+                                          fmaf(tanhf(al * y.z), w.z, bb.z), fmaf(tanhf(al * y.w), w.w, bb.w)));
+    }
+}
+
 // coef null: no averaging (x <- X).  norm_w null: no norm is made.
 extern "C" int aie_depth_average2(float* x, const float* a, int pa, long long sa, const float* b, int pb, long long sb,
                                   float mult, float* history, const float* coef, int depth, long long n,
@@ -200,13 +244,23 @@ extern "C" int aie_depth_average2(float* x, const float* a, int pa, long long sa
     if (depth < 0 || !a || pa < 1 || (coef && !history) || (norm_w && (!norm_b || !norm_alpha || !normed || D <= 0)))
         return AIE_BAD_ARG;
     if (!b) pb = 0;
-    const unsigned blocks = (unsigned)((n + 255) / 256);
-    if (norm_w && normed_dtype == AIE_BF16)
-        depth_average2_kernel<bf16><<<blocks, 256, 0, st>>>(x, a, pa, (size_t)sa, b, pb, (size_t)sb, mult, history, coef, depth,
-                                                           (size_t)n, norm_w, norm_b, norm_alpha, (bf16*)normed, D);
-    else
-        depth_average2_kernel<float><<<blocks, 256, 0, st>>>(x, a, pa, (size_t)sa, b, pb, (size_t)sb, mult, history, coef, depth,
-                                                            (size_t)n, norm_w, norm_b, norm_alpha, (float*)normed, D ? D : 1);
+    const bool bf = norm_w && normed_dtype == AIE_BF16;
+    auto al16 = [](const void* p) { return ((size_t)p & 15) == 0; };
+    const bool vec = n % 4 == 0 && (!norm_w || D % 4 == 0) && al16(x) && al16(a) && sa % 4 == 0 && (!pb || (al16(b) && sb % 4 == 0)) &&
+                     (!coef || al16(history)) && (!norm_w || (al16(norm_w) && al16(norm_b) && al16(normed)));
+#define GO(KERN, O, BLOCKS)                                                                                            \
+    KERN<O><<<BLOCKS, 256, 0, st>>>(x, a, pa, (size_t)sa, b, pb, (size_t)sb, mult, history, coef, depth, (size_t)n, norm_w,  \
+                                    norm_b, norm_alpha, (O*)normed, D > 0 ? D : 1)
+    if (vec) {
+        const unsigned blocks = (unsigned)((n / 4 + 255) / 256);
+        if (bf) GO(depth_average2_vec4_kernel, bf16, blocks);
+        else GO(depth_average2_vec4_kernel, float, blocks);
+    } else {
+        const unsigned blocks = (unsigned)((n + 255) / 256);
+        if (bf) GO(depth_average2_kernel, bf16, blocks);
+        else GO(depth_average2_kernel, float, blocks);
+    }
+#undef GO
     AIE_LAUNCH_CHECK();
 }
 

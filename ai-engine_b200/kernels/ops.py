@@ -855,13 +855,14 @@ def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_t
     if forget_lower is not None:
         if k is not None or decay_tok is None or forget_lower.dtype != torch.float32 or forget_lower.numel() != H * d:
             raise KernelError("linear_recurrence: the keyless form takes the gate's logits as decay_tok and no keys")
-        k = q                    # stands in for the shape checks below; the kernel gets no keys
+    keyless = forget_lower is not None
     if dt_raw is not None and (dt_raw.dtype != torch.float32 or dt_raw.stride(1) != 1 or dt_bias is None or a_log is None):
         raise KernelError("linear_recurrence: step sizes are a float32 view with their bias and rates")
     T = q.shape[0]
     ld = q.stride(0)
-    if (q.dtype != torch.float32 or k.dtype != torch.float32 or v.dtype != torch.float32 or k.stride(0) != ld
-            or v.stride(0) != ld or q.stride(1) != 1 or state.shape[1:] != (H, d, dv) or state.dtype != torch.float32):
+    if (q.dtype != torch.float32 or v.dtype != torch.float32 or v.stride(0) != ld or q.stride(1) != 1
+            or (not keyless and (k.dtype != torch.float32 or k.stride(0) != ld))
+            or state.shape[1:] != (H, d, dv) or state.dtype != torch.float32):
         raise KernelError("linear_recurrence: shapes or dtypes do not fit")
     out = torch.empty((T, H, dv), dtype=torch.float32, device=q.device)
     max_len = 0
@@ -880,7 +881,7 @@ def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_t
         max_len = SSD_MIN_TOKENS - 1                # the shorter portions and single tokens of the same step
     lib = library("linear_recurrence.cu")
     with region("linear_recurrence", _nb(out) + T * H * (2 * d + dv) * 4 + 2 * ctx.R * H * d * dv * 4, 4.0 * T * H * d * dv):
-        check(lib.aie_linear_recurrence(_p(q), _p(None if forget_lower is not None else k), _p(v), c_int(ld), _p(decay_tok),
+        check(lib.aie_linear_recurrence(_p(q), _p(k), _p(v), c_int(ld), _p(decay_tok),
                                         c_int(decay_tok.stride(0) if decay_tok is not None else 0), _p(decay_head),
                                         c_float(q_scale), c_float(k_scale), _p(state), _p(out), _p(ctx.q_start),
                                         _p(ctx.q_len), _p(ctx.slots), c_int(T), c_int(ctx.R), c_int(H), c_int(d), c_int(dv),
